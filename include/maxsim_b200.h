@@ -1,0 +1,191 @@
+/*
+ * maxsim_b200 -- C ABI of the sm_100a MaxSim library (libmaxsim_b200.so).
+ *
+ *   score(q, d) = sum_i max_j <q_i, d_j>
+ *
+ * One entry point per operator of the reference's torch extension.  The
+ * reference declares its nine operators in torch-ext/torch_binding.h:21-165
+ * (schemas in torch-ext/torch_binding.cpp:7-90) with torch::Tensor arguments;
+ * here every tensor becomes a device pointer plus explicit sizes so that the
+ * library carries no torch types.  Conventions shared by all entry points:
+ *
+ *   - every pointer is a device pointer on the CUDA device that is current
+ *     when the call is made; inputs are borrowed and never written;
+ *   - outputs are caller-allocated and need no initialisation: each call
+ *     defines every element of every output (argmax slots past a pair's query
+ *     length are 0, gradient rows nothing routes to are 0);
+ *   - `dtype` is a maxsim_dtype value and names the element type of
+ *     `queries` and `documents`; scores and gradients are always float,
+ *     argmax and all index arrays are int32_t;
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*; NULL is
+ *     the legacy default stream) and the call returns without synchronising;
+ *   - the return value is MAXSIM_OK or a negative maxsim_status;
+ *     maxsim_b200_last_error() gives a thread-local message for the last
+ *     failure.  No C++ exception crosses the boundary;
+ *   - empty problems (zero pairs) return MAXSIM_OK without launching.
+ *
+ * Tie and non-finite semantics (reference: maxsim_cuda/maxsim.cu:416-443,
+ * 517-528; tests/test_nan_inf.py:33-92): the first document token reaching
+ * the maximum wins; a NaN similarity never wins, so a NaN query token yields
+ * a -inf score with argmax 0 and a NaN document token is ignored.
+ */
+#ifndef MAXSIM_B200_H_
+#define MAXSIM_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define MAXSIM_API __attribute__((visibility("default")))
+#else
+#define MAXSIM_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum maxsim_dtype {
+  MAXSIM_F32 = 0,
+  MAXSIM_F16 = 1,
+  MAXSIM_BF16 = 2
+} maxsim_dtype;
+
+typedef enum maxsim_status {
+  MAXSIM_OK = 0,
+  MAXSIM_EINVAL = -1,       /* bad size, null pointer, misaligned base         */
+  MAXSIM_EUNSUPPORTED = -2, /* shape outside what the kernels implement        */
+  MAXSIM_ECUDA = -3,        /* a CUDA runtime call or launch failed            */
+  MAXSIM_EWORKSPACE = -4,   /* workspace missing or too small                  */
+  MAXSIM_EDEVICE = -5       /* a kernel reported a bounded wait that ran out   */
+} maxsim_status;
+
+/* Library identification and diagnostics (no reference counterpart). */
+MAXSIM_API const char* maxsim_b200_version(void);
+MAXSIM_API const char* maxsim_b200_last_error(void);
+/* Synchronises `stream`, then returns and clears the device-side status word
+ * that kernels set when one of their bounded waits gave up (0 = clean). */
+MAXSIM_API int maxsim_b200_device_status(void* stream);
+/* Number of kernel launches this process has enqueued through the library. */
+MAXSIM_API int64_t maxsim_b200_launch_count(void);
+/* Selects the forward implementation: 0 = automatic, 1 = force the portable
+ * SIMT kernel, 2 = force the warp-MMA streaming kernel where eligible,
+ * 3 = force the tcgen05 kernel where eligible.  For tests and profiling. */
+MAXSIM_API void maxsim_b200_set_forward_path(int path);
+
+/* ------------------------------------------------------------------------
+ * Packed pair grids.
+ * queries [total_q_tokens, dim], query_offsets [n_queries+1],
+ * documents [total_d_tokens, dim], document_offsets [n_documents+1],
+ * pair_query_ids / pair_document_ids [n_pairs].
+ * ---------------------------------------------------------------------- */
+
+/* Replaces maxsim_forward (torch-ext/torch_binding.h, host function
+ * maxsim_cuda/maxsim.cu:819-922).  scores [n_pairs]. */
+MAXSIM_API int maxsim_forward(const void* queries, const int32_t* query_offsets,
+                   const void* documents, const int32_t* document_offsets,
+                   const int32_t* pair_query_ids, const int32_t* pair_document_ids,
+                   float* scores,
+                   int64_t n_pairs, int64_t n_queries, int64_t n_documents,
+                   int64_t total_q_tokens, int64_t total_d_tokens,
+                   int64_t dim, int64_t max_q_len, int dtype, void* stream);
+
+/* Replaces maxsim_packed_forward_with_argmax (maxsim_cuda/maxsim.cu:2039-2108).
+ * scores [n_pairs], argmax [n_pairs, max_q_len]. */
+MAXSIM_API int maxsim_packed_forward_with_argmax(
+    const void* queries, const int32_t* query_offsets,
+    const void* documents, const int32_t* document_offsets,
+    const int32_t* pair_query_ids, const int32_t* pair_document_ids,
+    float* scores, int32_t* argmax,
+    int64_t n_pairs, int64_t n_queries, int64_t n_documents,
+    int64_t total_q_tokens, int64_t total_d_tokens,
+    int64_t dim, int64_t max_q_len, int dtype, void* stream);
+
+/* Replaces maxsim_packed_backward (maxsim_cuda/maxsim.cu:2201-2286).
+ * dscore [n_pairs]; grad_queries [total_q_tokens, dim] and
+ * grad_documents [total_d_tokens, dim], both float. */
+MAXSIM_API int maxsim_packed_backward(
+    const float* dscore,
+    const void* queries, const int32_t* query_offsets,
+    const void* documents, const int32_t* document_offsets,
+    const int32_t* pair_query_ids, const int32_t* pair_document_ids,
+    const int32_t* argmax,
+    float* grad_queries, float* grad_documents,
+    int64_t n_pairs, int64_t n_queries, int64_t n_documents,
+    int64_t total_q_tokens, int64_t total_d_tokens,
+    int64_t dim, int64_t max_q_len, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Padded candidates.
+ * queries [B*Lq_max, dim], query_lengths [B],
+ * documents [B*C*Ld_max, dim], doc_lengths [B*C].
+ * Pair p = b*C + c scores query b against document slab p.
+ * ---------------------------------------------------------------------- */
+
+/* Replaces maxsim_padded_forward (maxsim_cuda/maxsim.cu:924-1024).
+ * scores [B*C]. */
+MAXSIM_API int maxsim_padded_forward(const void* queries, const int32_t* query_lengths,
+                          const void* documents, const int32_t* doc_lengths,
+                          float* scores,
+                          int64_t B, int64_t C, int64_t Lq_max, int64_t Ld_max,
+                          int64_t dim, int dtype, void* stream);
+
+/* Replaces maxsim_padded_forward_with_argmax (maxsim_cuda/maxsim.cu:1036-1116).
+ * scores [B*C], argmax [B*C, Lq_max].  Unlike the reference this also accepts
+ * MAXSIM_F32 and shapes that are not multiples of 16. */
+MAXSIM_API int maxsim_padded_forward_with_argmax(
+    const void* queries, const int32_t* query_lengths,
+    const void* documents, const int32_t* doc_lengths,
+    float* scores, int32_t* argmax,
+    int64_t B, int64_t C, int64_t Lq_max, int64_t Ld_max,
+    int64_t dim, int dtype, void* stream);
+
+/* Replaces maxsim_padded_backward (maxsim_cuda/maxsim.cu:1124-1210).
+ * dscore [B*C]; grad_queries [B*Lq_max, dim], grad_documents [B*C*Ld_max, dim]. */
+MAXSIM_API int maxsim_padded_backward(
+    const float* dscore,
+    const void* queries, const void* documents,
+    const int32_t* query_lengths, const int32_t* doc_lengths,
+    const int32_t* argmax,
+    float* grad_queries, float* grad_documents,
+    int64_t B, int64_t C, int64_t Lq_max, int64_t Ld_max,
+    int64_t dim, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------
+ * Contrastive all-pairs.
+ * queries [Nq, Lq, dim] rectangular, documents [total_d_tokens, dim] packed,
+ * document_offsets [Nb+1].  Pair p = q*Nb + d.
+ * ---------------------------------------------------------------------- */
+
+/* Replaces maxsim_contrastive_forward (maxsim_cuda/maxsim.cu:1718-1779).
+ * scores [Nq, Nb]. */
+MAXSIM_API int maxsim_contrastive_forward(const void* queries, const void* documents,
+                               const int32_t* document_offsets,
+                               float* scores,
+                               int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim,
+                               int64_t total_d_tokens, int dtype, void* stream);
+
+/* Replaces maxsim_contrastive_forward_with_argmax
+ * (maxsim_cuda/maxsim.cu:1650-1716).  scores [Nq, Nb], argmax [Nq, Nb, Lq]. */
+MAXSIM_API int maxsim_contrastive_forward_with_argmax(
+    const void* queries, const void* documents,
+    const int32_t* document_offsets,
+    float* scores, int32_t* argmax,
+    int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim,
+    int64_t total_d_tokens, int dtype, void* stream);
+
+/* Replaces maxsim_contrastive_backward (maxsim_cuda/maxsim.cu:1856-1920).
+ * dscore [Nq, Nb]; grad_queries [Nq, Lq, dim], grad_documents
+ * [total_d_tokens, dim]. */
+MAXSIM_API int maxsim_contrastive_backward(
+    const float* dscore,
+    const void* queries, const void* documents,
+    const int32_t* document_offsets, const int32_t* argmax,
+    float* grad_queries, float* grad_documents,
+    int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim,
+    int64_t total_d_tokens, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MAXSIM_B200_H_ */

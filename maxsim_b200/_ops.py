@@ -1,0 +1,401 @@
+"""The nine operators, as Python callables over the C ABI.
+
+``ops`` exposes exactly the callables the reference's Python layer looks up on
+``maxsim._ops.ops`` (``torch-ext/torch_binding.cpp:7-90``; the development
+binding ``maxsim_cuda/dev_binding.cpp:82-104`` and ``tests/conftest.py:133-145``
+build the same namespace): same names, positional arguments, return shapes and
+dtypes.  Each callable allocates its outputs with torch, hands raw device
+pointers and the current CUDA stream to ``libmaxsim_b200.so`` through ctypes
+and raises ``RuntimeError`` on a non-zero status, the way ``TORCH_CHECK`` does
+in the reference.
+
+There is no CPU path: a tensor that is not on a CUDA device, or a missing
+library, is an error.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import types
+from ctypes import c_char_p, c_int, c_int64, c_void_p
+from typing import Tuple
+
+import torch
+
+from . import _build
+
+_DTYPE_CODE = {torch.float32: 0, torch.float16: 1, torch.bfloat16: 2}
+
+_lib = None
+
+_I64 = c_int64
+_P = c_void_p
+
+_SIGNATURES = {
+    "maxsim_b200_version": (c_char_p, []),
+    "maxsim_b200_last_error": (c_char_p, []),
+    "maxsim_b200_device_status": (c_int, [_P]),
+    "maxsim_b200_launch_count": (c_int64, []),
+    "maxsim_b200_set_forward_path": (None, [c_int]),
+    "maxsim_forward": (c_int, [_P] * 7 + [_I64] * 7 + [c_int, _P]),
+    "maxsim_packed_forward_with_argmax": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
+    "maxsim_packed_backward": (c_int, [_P] * 10 + [_I64] * 7 + [c_int, _P]),
+    "maxsim_padded_forward": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, _P]),
+    "maxsim_padded_forward_with_argmax": (c_int, [_P] * 6 + [_I64] * 5 + [c_int, _P]),
+    "maxsim_padded_backward": (c_int, [_P] * 8 + [_I64] * 5 + [c_int, _P]),
+    "maxsim_contrastive_forward": (c_int, [_P] * 4 + [_I64] * 5 + [c_int, _P]),
+    "maxsim_contrastive_forward_with_argmax": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, _P]),
+    "maxsim_contrastive_backward": (c_int, [_P] * 7 + [_I64] * 5 + [c_int, _P]),
+}
+
+EXPORTED_SYMBOLS = tuple(_SIGNATURES)
+
+
+def load_library() -> ctypes.CDLL:
+    """Load (building first if the sources changed and nvcc is present)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if not _build.is_current():
+        try:
+            _build.build()
+        except RuntimeError as exc:
+            if not path.exists():
+                raise RuntimeError(
+                    f"libmaxsim_b200.so is not built and could not be built here: {exc}. "
+                    "Run `python -m maxsim_b200._build` on a machine with nvcc."
+                ) from exc
+    lib = ctypes.CDLL(str(path))
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def library_path() -> str:
+    return str(_build.LIB_PATH)
+
+
+def launch_count() -> int:
+    return int(load_library().maxsim_b200_launch_count())
+
+
+def set_forward_path(path: int) -> None:
+    load_library().maxsim_b200_set_forward_path(int(path))
+
+
+def device_status(device=None) -> int:
+    """Synchronise the current stream and return the kernels' status word."""
+    with torch.cuda.device(device):
+        return int(load_library().maxsim_b200_device_status(_stream_ptr()))
+
+
+def _stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t: torch.Tensor) -> int:
+    return t.data_ptr() if t.numel() else 0
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    if dev.type != "cuda":
+        raise RuntimeError(
+            f"queries must be a CUDA tensor (maxsim_b200 has no CPU path); got device {dev}")
+    for t in tensors[1:]:
+        if t.device != dev:
+            raise RuntimeError(f"all inputs must share a device; got {dev} and {t.device}")
+    return dev
+
+
+def _code(t: torch.Tensor) -> int:
+    try:
+        return _DTYPE_CODE[t.dtype]
+    except KeyError:
+        raise RuntimeError(
+            f"queries/documents dtype must be float32, float16, or bfloat16; got {t.dtype}") from None
+
+
+def _check(rc: int, what: str) -> None:
+    if rc != 0:
+        msg = load_library().maxsim_b200_last_error().decode("utf-8", "replace")
+        raise RuntimeError(f"{what} failed (status {rc}): {msg}")
+
+
+def _i32(t: torch.Tensor) -> torch.Tensor:
+    return t.contiguous().to(torch.int32)
+
+
+def _same_float(q: torch.Tensor, d: torch.Tensor) -> None:
+    if q.dtype != d.dtype:
+        raise RuntimeError("queries and documents must have the same dtype")
+
+
+# ---------------------------------------------------------------------------
+# packed
+# ---------------------------------------------------------------------------
+
+def _packed_args(queries, query_offsets, documents, document_offsets,
+                 pair_query_ids, pair_document_ids):
+    if queries.dim() != 2 or documents.dim() != 2:
+        raise RuntimeError("queries/documents must be 2-D [tokens, dim]")
+    if queries.shape[1] != documents.shape[1]:
+        raise RuntimeError("queries.dim must match documents.dim")
+    _same_float(queries, documents)
+    q = queries.contiguous()
+    d = documents.contiguous()
+    return (q, _i32(query_offsets), d, _i32(document_offsets),
+            _i32(pair_query_ids), _i32(pair_document_ids))
+
+
+def maxsim_forward(queries, query_offsets, documents, document_offsets,
+                   pair_query_ids, pair_document_ids, max_q_len) -> torch.Tensor:
+    dev = _require_cuda(queries, query_offsets, documents, document_offsets,
+                        pair_query_ids, pair_document_ids)
+    q, qoff, d, doff, pq, pd = _packed_args(queries, query_offsets, documents,
+                                            document_offsets, pair_query_ids, pair_document_ids)
+    n_pairs = pq.shape[0]
+    scores = torch.empty((n_pairs,), dtype=torch.float32, device=dev)
+    if n_pairs == 0:
+        return scores
+    max_q_len = int(max_q_len)
+    if max_q_len < 0:
+        # the reference infers the bound from query_offsets when given a negative value
+        max_q_len = int((qoff[1:] - qoff[:-1]).max().item())
+    if max_q_len <= 0:
+        raise RuntimeError(f"max_q_len must be > 0; got {max_q_len}")
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_forward(
+            _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd), _ptr(scores),
+            n_pairs, qoff.shape[0] - 1, doff.shape[0] - 1, q.shape[0], d.shape[0],
+            q.shape[1], max_q_len, _code(q), _stream_ptr())
+    _check(rc, "maxsim_forward")
+    return scores
+
+
+def maxsim_packed_forward_with_argmax(queries, query_offsets, documents, document_offsets,
+                                      pair_query_ids, pair_document_ids,
+                                      max_q_len) -> Tuple[torch.Tensor, torch.Tensor]:
+    dev = _require_cuda(queries, query_offsets, documents, document_offsets,
+                        pair_query_ids, pair_document_ids)
+    q, qoff, d, doff, pq, pd = _packed_args(queries, query_offsets, documents,
+                                            document_offsets, pair_query_ids, pair_document_ids)
+    max_q_len = int(max_q_len)
+    if max_q_len <= 0:
+        raise RuntimeError(f"max_q_len must be > 0; got {max_q_len}")
+    n_pairs = pq.shape[0]
+    scores = torch.empty((n_pairs,), dtype=torch.float32, device=dev)
+    argmax = torch.empty((n_pairs, max_q_len), dtype=torch.int32, device=dev)
+    if n_pairs == 0:
+        return scores, argmax
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_packed_forward_with_argmax(
+            _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd),
+            _ptr(scores), _ptr(argmax),
+            n_pairs, qoff.shape[0] - 1, doff.shape[0] - 1, q.shape[0], d.shape[0],
+            q.shape[1], max_q_len, _code(q), _stream_ptr())
+    _check(rc, "maxsim_packed_forward_with_argmax")
+    return scores, argmax
+
+
+def maxsim_packed_backward(dscore, queries, query_offsets, documents, document_offsets,
+                           pair_query_ids, pair_document_ids, argmax,
+                           max_q_len) -> Tuple[torch.Tensor, torch.Tensor]:
+    dev = _require_cuda(queries, dscore, query_offsets, documents, document_offsets,
+                        pair_query_ids, pair_document_ids, argmax)
+    q, qoff, d, doff, pq, pd = _packed_args(queries, query_offsets, documents,
+                                            document_offsets, pair_query_ids, pair_document_ids)
+    g = dscore.contiguous().to(torch.float32)
+    a = argmax.contiguous().to(torch.int32)
+    n_pairs = pq.shape[0]
+    max_q_len = int(max_q_len)
+    if g.numel() != n_pairs:
+        raise RuntimeError("dscore must have one entry per pair")
+    if tuple(a.shape) != (n_pairs, max_q_len):
+        raise RuntimeError("argmax must have shape [num_pairs, max_q_len]")
+    dq = torch.empty(q.shape, dtype=torch.float32, device=dev)
+    dd = torch.empty(d.shape, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_packed_backward(
+            _ptr(g), _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd), _ptr(a),
+            _ptr(dq), _ptr(dd),
+            n_pairs, qoff.shape[0] - 1, doff.shape[0] - 1, q.shape[0], d.shape[0],
+            q.shape[1], max(max_q_len, 1), _code(q), _stream_ptr())
+    _check(rc, "maxsim_packed_backward")
+    return dq, dd
+
+
+# ---------------------------------------------------------------------------
+# padded
+# ---------------------------------------------------------------------------
+
+def _padded_args(queries, query_lengths, documents, doc_lengths, Lq_max, Ld_max, C):
+    if queries.dim() != 2 or documents.dim() != 2:
+        raise RuntimeError("queries/documents must be 2-D")
+    if queries.shape[1] != documents.shape[1]:
+        raise RuntimeError("queries.dim must match documents.dim")
+    _same_float(queries, documents)
+    Lq_max, Ld_max, C = int(Lq_max), int(Ld_max), int(C)
+    if Lq_max <= 0 or Ld_max <= 0 or C <= 0:
+        raise RuntimeError("Lq_max/Ld_max/num_candidates must all be > 0")
+    q = queries.contiguous()
+    d = documents.contiguous()
+    if q.shape[0] % Lq_max != 0:
+        raise RuntimeError("queries rows must be a multiple of Lq_max")
+    if d.shape[0] % Ld_max != 0:
+        raise RuntimeError("documents rows must be a multiple of Ld_max")
+    B = q.shape[0] // Lq_max
+    if d.shape[0] // Ld_max != B * C:
+        raise RuntimeError("documents shape inconsistent with B * num_candidates")
+    qlen = _i32(query_lengths)
+    dlen = _i32(doc_lengths)
+    if qlen.numel() != B or dlen.numel() != B * C:
+        raise RuntimeError("length tensors inconsistent with B and num_candidates")
+    return q, qlen, d, dlen, B, C, Lq_max, Ld_max
+
+
+def maxsim_padded_forward(queries, query_lengths, documents, doc_lengths,
+                          Lq_max, Ld_max, num_candidates) -> torch.Tensor:
+    dev = _require_cuda(queries, query_lengths, documents, doc_lengths)
+    q, qlen, d, dlen, B, C, Lq_max, Ld_max = _padded_args(
+        queries, query_lengths, documents, doc_lengths, Lq_max, Ld_max, num_candidates)
+    scores = torch.empty((B * C,), dtype=torch.float32, device=dev)
+    if B * C == 0:
+        return scores
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_padded_forward(
+            _ptr(q), _ptr(qlen), _ptr(d), _ptr(dlen), _ptr(scores),
+            B, C, Lq_max, Ld_max, q.shape[1], _code(q), _stream_ptr())
+    _check(rc, "maxsim_padded_forward")
+    return scores
+
+
+def maxsim_padded_forward_with_argmax(queries, query_lengths, documents, doc_lengths,
+                                      Lq_max, Ld_max, num_candidates):
+    dev = _require_cuda(queries, query_lengths, documents, doc_lengths)
+    q, qlen, d, dlen, B, C, Lq_max, Ld_max = _padded_args(
+        queries, query_lengths, documents, doc_lengths, Lq_max, Ld_max, num_candidates)
+    scores = torch.empty((B * C,), dtype=torch.float32, device=dev)
+    argmax = torch.empty((B * C, Lq_max), dtype=torch.int32, device=dev)
+    if B * C == 0:
+        return scores, argmax
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_padded_forward_with_argmax(
+            _ptr(q), _ptr(qlen), _ptr(d), _ptr(dlen), _ptr(scores), _ptr(argmax),
+            B, C, Lq_max, Ld_max, q.shape[1], _code(q), _stream_ptr())
+    _check(rc, "maxsim_padded_forward_with_argmax")
+    return scores, argmax
+
+
+def maxsim_padded_backward(dscore, queries, documents, query_lengths, doc_lengths, argmax,
+                           Lq_max, Ld_max, num_candidates):
+    dev = _require_cuda(queries, dscore, documents, query_lengths, doc_lengths, argmax)
+    q, qlen, d, dlen, B, C, Lq_max, Ld_max = _padded_args(
+        queries, query_lengths, documents, doc_lengths, Lq_max, Ld_max, num_candidates)
+    g = dscore.contiguous().to(torch.float32)
+    a = argmax.contiguous().to(torch.int32)
+    if g.numel() != B * C:
+        raise RuntimeError("dscore must have B * num_candidates entries")
+    if a.numel() != B * C * Lq_max:
+        raise RuntimeError("argmax must have shape [B * num_candidates, Lq_max]")
+    dq = torch.empty(q.shape, dtype=torch.float32, device=dev)
+    dd = torch.empty(d.shape, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_padded_backward(
+            _ptr(g), _ptr(q), _ptr(d), _ptr(qlen), _ptr(dlen), _ptr(a), _ptr(dq), _ptr(dd),
+            B, C, Lq_max, Ld_max, q.shape[1], _code(q), _stream_ptr())
+    _check(rc, "maxsim_padded_backward")
+    return dq, dd
+
+
+# ---------------------------------------------------------------------------
+# contrastive
+# ---------------------------------------------------------------------------
+
+def _contrastive_args(queries, documents, document_offsets):
+    if queries.dim() != 3:
+        raise RuntimeError("queries must be [Nq, Lq, D]")
+    if documents.dim() != 2:
+        raise RuntimeError("documents must be [total_d_tokens, D]")
+    if document_offsets.dim() != 1:
+        raise RuntimeError("document_offsets must be 1-D")
+    if queries.shape[2] != documents.shape[1]:
+        raise RuntimeError("queries.D must match documents.D")
+    _same_float(queries, documents)
+    q = queries.contiguous()
+    d = documents.contiguous()
+    off = _i32(document_offsets)
+    Nq, Lq, dim = q.shape
+    Nb = off.shape[0] - 1
+    if Nb < 0:
+        raise RuntimeError("document_offsets must have at least 1 element")
+    if Lq <= 0:
+        raise RuntimeError("Lq must be > 0")
+    if dim <= 0:
+        raise RuntimeError("dim must be > 0")
+    return q, d, off, Nq, Lq, Nb, dim
+
+
+def maxsim_contrastive_forward(queries, documents, document_offsets) -> torch.Tensor:
+    dev = _require_cuda(queries, documents, document_offsets)
+    q, d, off, Nq, Lq, Nb, dim = _contrastive_args(queries, documents, document_offsets)
+    scores = torch.empty((Nq, Nb), dtype=torch.float32, device=dev)
+    if Nq * Nb == 0:
+        return scores
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_contrastive_forward(
+            _ptr(q), _ptr(d), _ptr(off), _ptr(scores),
+            Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
+    _check(rc, "maxsim_contrastive_forward")
+    return scores
+
+
+def maxsim_contrastive_forward_with_argmax(queries, documents, document_offsets):
+    dev = _require_cuda(queries, documents, document_offsets)
+    q, d, off, Nq, Lq, Nb, dim = _contrastive_args(queries, documents, document_offsets)
+    scores = torch.empty((Nq, Nb), dtype=torch.float32, device=dev)
+    argmax = torch.empty((Nq, Nb, Lq), dtype=torch.int32, device=dev)
+    if Nq * Nb == 0:
+        return scores, argmax
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_contrastive_forward_with_argmax(
+            _ptr(q), _ptr(d), _ptr(off), _ptr(scores), _ptr(argmax),
+            Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
+    _check(rc, "maxsim_contrastive_forward_with_argmax")
+    return scores, argmax
+
+
+def maxsim_contrastive_backward(dscore, queries, documents, document_offsets, argmax):
+    dev = _require_cuda(queries, dscore, documents, document_offsets, argmax)
+    q, d, off, Nq, Lq, Nb, dim = _contrastive_args(queries, documents, document_offsets)
+    g = dscore.contiguous().to(torch.float32)
+    a = argmax.contiguous().to(torch.int32)
+    if tuple(g.shape) != (Nq, Nb):
+        raise RuntimeError("dscore must have shape [Nq, Nb]")
+    if tuple(a.shape) != (Nq, Nb, Lq):
+        raise RuntimeError("argmax must have shape [Nq, Nb, Lq]")
+    dq = torch.empty(q.shape, dtype=torch.float32, device=dev)
+    dd = torch.empty(d.shape, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_contrastive_backward(
+            _ptr(g), _ptr(q), _ptr(d), _ptr(off), _ptr(a), _ptr(dq), _ptr(dd),
+            Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
+    _check(rc, "maxsim_contrastive_backward")
+    return dq, dd
+
+
+ops = types.SimpleNamespace(
+    maxsim_forward=maxsim_forward,
+    maxsim_padded_forward=maxsim_padded_forward,
+    maxsim_padded_forward_with_argmax=maxsim_padded_forward_with_argmax,
+    maxsim_padded_backward=maxsim_padded_backward,
+    maxsim_packed_forward_with_argmax=maxsim_packed_forward_with_argmax,
+    maxsim_packed_backward=maxsim_packed_backward,
+    maxsim_contrastive_forward=maxsim_contrastive_forward,
+    maxsim_contrastive_forward_with_argmax=maxsim_contrastive_forward_with_argmax,
+    maxsim_contrastive_backward=maxsim_contrastive_backward,
+)

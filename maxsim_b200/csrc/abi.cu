@@ -1,0 +1,409 @@
+// extern "C" entry points of libmaxsim_b200.so and the host-side dispatch.
+// No torch headers: the boundary is plain pointers, sizes and a stream.
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <string>
+#include <type_traits>
+
+#include "../../include/maxsim_b200.h"
+#include "bwd.cuh"
+#include "common.cuh"
+#include "fwd_mma.cuh"
+#include "fwd_simt.cuh"
+#include "fwd_tc05.cuh"
+
+namespace maxsim {
+
+namespace {
+
+thread_local std::string t_last_error;
+std::atomic<int64_t> g_launches{0};
+std::atomic<int> g_forward_path{0};
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  t_last_error = buf;
+  return code;
+}
+
+#define MAXSIM_CUDA(expr)                                                         \
+  do {                                                                            \
+    cudaError_t e_ = (expr);                                                      \
+    if (e_ != cudaSuccess)                                                        \
+      return fail(MAXSIM_ECUDA, "%s failed: %s", #expr, cudaGetErrorString(e_)); \
+  } while (0)
+
+int launch_check(const char* what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(MAXSIM_ECUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+  return MAXSIM_OK;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+bool valid_dtype(int dtype) { return dtype == MAXSIM_F32 || dtype == MAXSIM_F16 || dtype == MAXSIM_BF16; }
+
+// ---------------------------------------------------------------------------
+// Forward dispatch
+// ---------------------------------------------------------------------------
+template <typename T, int LAYOUT, bool ARGMAX>
+int launch_simt(const PairTable& t, float* scores, int32_t* argmax, cudaStream_t st) {
+  const int dimp = (t.dim + 7) & ~7;
+  const size_t smem = ((size_t)kSimtRows * dimp + 8 * kSimtRows) * sizeof(float);
+  if (smem > 200 * 1024) return fail(MAXSIM_EUNSUPPORTED, "dim=%d too large for the SIMT kernel", t.dim);
+  auto kern = fwd_simt_kernel<T, LAYOUT, ARGMAX>;
+  if (smem > 48 * 1024)
+    MAXSIM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int elems16 = 16 / (int)sizeof(T);
+  const int vec_ok = (t.dim % elems16 == 0) && aligned16(t.documents);
+  const int64_t grid = t.n_pairs < (1 << 22) ? t.n_pairs : (1 << 22);
+  kern<<<(unsigned)grid, kSimtThreads, smem, st>>>(t, scores, argmax, vec_ok);
+  return launch_check("fwd_simt_kernel");
+}
+
+template <typename T, int DIM, int LAYOUT, bool ARGMAX>
+int launch_mma_dim(const PairTable& t, float* scores, int32_t* argmax, cudaStream_t st) {
+  auto kern = fwd_mma_kernel<T, DIM, LAYOUT, ARGMAX>;
+  constexpr size_t smem = mma_smem_bytes<DIM>();
+  static bool configured[64] = {false};
+  int dev = 0;
+  MAXSIM_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    MAXSIM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int sms = sm_count();
+  const int64_t warps_full = (int64_t)sms * kMmaWarps;
+  int ppc = (int)(t.n_pairs / (warps_full * 4));
+  if (ppc < 1) ppc = 1;
+  if (ppc > 8) ppc = 8;
+  const int64_t n_chunks = (t.n_pairs + ppc - 1) / ppc;
+  int64_t grid = (n_chunks + kMmaWarps - 1) / kMmaWarps;
+  if (grid > sms) grid = sms;
+  if (grid < 1) grid = 1;
+  kern<<<(unsigned)grid, kMmaThreads, smem, st>>>(t, scores, argmax, ppc);
+  return launch_check("fwd_mma_kernel");
+}
+
+template <typename T, int LAYOUT, bool ARGMAX>
+int launch_mma(const PairTable& t, float* scores, int32_t* argmax, cudaStream_t st) {
+  switch (t.dim) {
+    case 32: return launch_mma_dim<T, 32, LAYOUT, ARGMAX>(t, scores, argmax, st);
+    case 64: return launch_mma_dim<T, 64, LAYOUT, ARGMAX>(t, scores, argmax, st);
+    case 96: return launch_mma_dim<T, 96, LAYOUT, ARGMAX>(t, scores, argmax, st);
+    case 128: return launch_mma_dim<T, 128, LAYOUT, ARGMAX>(t, scores, argmax, st);
+    default: return fail(MAXSIM_EUNSUPPORTED, "warp-MMA kernel does not take dim=%d", t.dim);
+  }
+}
+
+bool mma_eligible(const PairTable& t, int dtype) {
+  if (dtype == MAXSIM_F32) return false;
+  if (!(t.dim == 32 || t.dim == 64 || t.dim == 96 || t.dim == 128)) return false;
+  if (!aligned16(t.queries) || !aligned16(t.documents)) return false;
+  if (t.n_pairs >= (1ll << 31)) return false;
+  return true;
+}
+
+template <int LAYOUT, bool ARGMAX>
+int run_forward(const PairTable& t, float* scores, int32_t* argmax, int dtype, void* stream) {
+  if (!valid_dtype(dtype)) return fail(MAXSIM_EINVAL, "unknown dtype code %d", dtype);
+  if (t.n_pairs < 0 || t.dim <= 0 || t.q_slots <= 0)
+    return fail(MAXSIM_EINVAL, "sizes must be positive (pairs=%lld dim=%d q_slots=%d)",
+                (long long)t.n_pairs, t.dim, t.q_slots);
+  if (t.n_pairs == 0) return MAXSIM_OK;
+  if (!t.queries || !t.documents || !scores || (ARGMAX && !argmax))
+    return fail(MAXSIM_EINVAL, "null pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int path = g_forward_path.load(std::memory_order_relaxed);
+
+  if (LAYOUT == kContrastive && path != 1 && path != 2 && tc05_eligible(t, dtype)) {
+    return launch_tc05<ARGMAX>(t, scores, argmax, dtype, st);
+  }
+  if (path == 3 && LAYOUT == kContrastive)
+    return fail(MAXSIM_EUNSUPPORTED, "tcgen05 kernel forced but shape not eligible");
+
+  if (path != 1 && mma_eligible(t, dtype)) {
+    if (dtype == MAXSIM_F16) return launch_mma<__half, LAYOUT, ARGMAX>(t, scores, argmax, st);
+    return launch_mma<__nv_bfloat16, LAYOUT, ARGMAX>(t, scores, argmax, st);
+  }
+  switch (dtype) {
+    case MAXSIM_F32: return launch_simt<float, LAYOUT, ARGMAX>(t, scores, argmax, st);
+    case MAXSIM_F16: return launch_simt<__half, LAYOUT, ARGMAX>(t, scores, argmax, st);
+    default: return launch_simt<__nv_bfloat16, LAYOUT, ARGMAX>(t, scores, argmax, st);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Backward dispatch
+// ---------------------------------------------------------------------------
+template <typename T, int LAYOUT>
+int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argmax, float* dq,
+                   float* dd, int64_t q_rows, int64_t d_rows, int64_t Nq, cudaStream_t st) {
+  const int dim = t.dim;
+  const int vec_ok = (dim % 4 == 0) && aligned16(t.queries) && aligned16(t.documents) &&
+                     aligned16(dq) && aligned16(dd);
+  const unsigned threads = kBwdWarps * 32;
+  if constexpr (LAYOUT == kPacked) {
+    MAXSIM_CUDA(cudaMemsetAsync(dq, 0, (size_t)q_rows * dim * sizeof(float), st));
+    MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
+    if (t.n_pairs == 0) return MAXSIM_OK;
+    const int64_t grid = (t.n_pairs + kBwdWarps - 1) / kBwdWarps;
+    bwd_route_atomic_kernel<T, LAYOUT, true, true><<<(unsigned)grid, threads, 0, st>>>(
+        t, dscore, argmax, dq, dd, vec_ok);
+    return launch_check("bwd_route_atomic_kernel");
+  } else {
+    if (t.n_pairs == 0) {
+      MAXSIM_CUDA(cudaMemsetAsync(dq, 0, (size_t)q_rows * dim * sizeof(float), st));
+      MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
+      return MAXSIM_OK;
+    }
+    {
+      const int64_t grid = (q_rows + kBwdWarps - 1) / kBwdWarps;
+      bwd_dq_gather_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq,
+                                                                           q_rows, vec_ok);
+      int rc = launch_check("bwd_dq_gather_kernel");
+      if (rc) return rc;
+    }
+    if constexpr (LAYOUT == kPadded) {
+      const int64_t grid = (t.n_pairs + kBwdWarps - 1) / kBwdWarps;
+      bwd_dd_padded_kernel<T><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dd, vec_ok);
+      return launch_check("bwd_dd_padded_kernel");
+    } else {
+      const size_t smem = (size_t)kSegTokens * dim * sizeof(float);
+      if (smem <= 200 * 1024) {
+        // longest document decides how many token chunks each document gets
+        // (documents shorter than that exit early).  The host does not know
+        // the lengths, so size by the worst case total_d_tokens bound.
+        auto kern = bwd_dd_contrastive_kernel<T>;
+        if (smem > 48 * 1024)
+          MAXSIM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // d_rows tokens over Nb documents, each >= 1 token: no document is
+        // longer than d_rows - (Nb - 1).
+        const int64_t Nb = t.C;
+        int64_t longest = d_rows - (Nb - 1);
+        if (longest < 1) longest = 1;
+        int64_t max_chunks = (longest + kSegTokens - 1) / kSegTokens;
+        // Launch-size guard: very skewed batches fall back to atomics.
+        if (max_chunks * Nb <= (1ll << 24) && max_chunks <= 64) {
+          kern<<<(unsigned)(max_chunks * Nb), kSegWarps * 32, smem, st>>>(t, dscore, argmax, dd, Nq,
+                                                                          (int)max_chunks, vec_ok);
+          return launch_check("bwd_dd_contrastive_kernel");
+        }
+      }
+      MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
+      const int64_t grid = (t.n_pairs + kBwdWarps - 1) / kBwdWarps;
+      bwd_route_atomic_kernel<T, LAYOUT, false, true><<<(unsigned)grid, threads, 0, st>>>(
+          t, dscore, argmax, dq, dd, vec_ok);
+      return launch_check("bwd_route_atomic_kernel");
+    }
+  }
+}
+
+template <int LAYOUT>
+int run_backward(const PairTable& t, const float* dscore, const int32_t* argmax, float* dq,
+                 float* dd, int64_t q_rows, int64_t d_rows, int64_t Nq, int dtype, void* stream) {
+  if (!valid_dtype(dtype)) return fail(MAXSIM_EINVAL, "unknown dtype code %d", dtype);
+  if (t.dim <= 0 || t.q_slots <= 0 || t.n_pairs < 0 || q_rows < 0 || d_rows < 0)
+    return fail(MAXSIM_EINVAL, "sizes must be positive");
+  if ((q_rows && !dq) || (d_rows && !dd)) return fail(MAXSIM_EINVAL, "null gradient pointer");
+  if (t.n_pairs && (!dscore || !argmax || !t.queries || !t.documents))
+    return fail(MAXSIM_EINVAL, "null pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case MAXSIM_F32: return run_backward_t<float, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
+    case MAXSIM_F16: return run_backward_t<__half, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
+    default: return run_backward_t<__nv_bfloat16, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
+  }
+}
+
+PairTable packed_table(const void* q, const int32_t* qoff, const void* d, const int32_t* doff,
+                       const int32_t* pq, const int32_t* pd, int64_t n_pairs, int64_t dim,
+                       int64_t max_q_len) {
+  PairTable t{};
+  t.queries = q; t.documents = d;
+  t.ia = qoff; t.ib = doff; t.ic = pq; t.id = pd;
+  t.n_pairs = n_pairs; t.dim = (int32_t)dim; t.q_slots = (int32_t)max_q_len;
+  t.Ld_max = 0; t.C = 1;
+  return t;
+}
+
+PairTable padded_table(const void* q, const int32_t* qlen, const void* d, const int32_t* dlen,
+                       int64_t B, int64_t C, int64_t Lq_max, int64_t Ld_max, int64_t dim) {
+  PairTable t{};
+  t.queries = q; t.documents = d;
+  t.ia = qlen; t.ib = dlen; t.ic = nullptr; t.id = nullptr;
+  t.n_pairs = B * C; t.dim = (int32_t)dim; t.q_slots = (int32_t)Lq_max;
+  t.Ld_max = (int32_t)Ld_max; t.C = (int32_t)(C > 0 ? C : 1);
+  return t;
+}
+
+PairTable contrastive_table(const void* q, const void* d, const int32_t* doff, int64_t Nq,
+                            int64_t Lq, int64_t Nb, int64_t dim) {
+  PairTable t{};
+  t.queries = q; t.documents = d;
+  t.ia = nullptr; t.ib = doff; t.ic = nullptr; t.id = nullptr;
+  t.n_pairs = Nq * Nb; t.dim = (int32_t)dim; t.q_slots = (int32_t)Lq;
+  t.Ld_max = 0; t.C = (int32_t)(Nb > 0 ? Nb : 1);
+  return t;
+}
+
+bool fits_i32(int64_t v) { return v >= 0 && v < (1ll << 31); }
+
+}  // namespace
+}  // namespace maxsim
+
+using namespace maxsim;
+
+extern "C" {
+
+const char* maxsim_b200_version(void) { return "maxsim_b200 0.1 (sm_100a)"; }
+const char* maxsim_b200_last_error(void) { return t_last_error.c_str(); }
+int64_t maxsim_b200_launch_count(void) { return g_launches.load(); }
+void maxsim_b200_set_forward_path(int path) { g_forward_path.store(path); }
+
+int maxsim_b200_device_status(void* stream) {
+  int v = 0, zero = 0;
+  if (cudaStreamSynchronize(static_cast<cudaStream_t>(stream)) != cudaSuccess) return MAXSIM_ECUDA;
+  if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return MAXSIM_ECUDA;
+  if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
+  return v;
+}
+
+int maxsim_forward(const void* queries, const int32_t* query_offsets, const void* documents,
+                   const int32_t* document_offsets, const int32_t* pair_query_ids,
+                   const int32_t* pair_document_ids, float* scores, int64_t n_pairs,
+                   int64_t n_queries, int64_t n_documents, int64_t total_q_tokens,
+                   int64_t total_d_tokens, int64_t dim, int64_t max_q_len, int dtype,
+                   void* stream) {
+  (void)n_queries; (void)n_documents;
+  if (!fits_i32(dim) || !fits_i32(max_q_len) || !fits_i32(total_q_tokens) || !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
+  if (max_q_len <= 0) return fail(MAXSIM_EINVAL, "max_q_len must be > 0; got %lld", (long long)max_q_len);
+  PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
+                             pair_document_ids, n_pairs, dim, max_q_len);
+  return run_forward<kPacked, false>(t, scores, nullptr, dtype, stream);
+}
+
+int maxsim_packed_forward_with_argmax(const void* queries, const int32_t* query_offsets,
+                                      const void* documents, const int32_t* document_offsets,
+                                      const int32_t* pair_query_ids,
+                                      const int32_t* pair_document_ids, float* scores,
+                                      int32_t* argmax, int64_t n_pairs, int64_t n_queries,
+                                      int64_t n_documents, int64_t total_q_tokens,
+                                      int64_t total_d_tokens, int64_t dim, int64_t max_q_len,
+                                      int dtype, void* stream) {
+  (void)n_queries; (void)n_documents;
+  if (!fits_i32(dim) || !fits_i32(max_q_len) || !fits_i32(total_q_tokens) || !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
+  if (max_q_len <= 0) return fail(MAXSIM_EINVAL, "max_q_len must be > 0; got %lld", (long long)max_q_len);
+  PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
+                             pair_document_ids, n_pairs, dim, max_q_len);
+  return run_forward<kPacked, true>(t, scores, argmax, dtype, stream);
+}
+
+int maxsim_packed_backward(const float* dscore, const void* queries, const int32_t* query_offsets,
+                           const void* documents, const int32_t* document_offsets,
+                           const int32_t* pair_query_ids, const int32_t* pair_document_ids,
+                           const int32_t* argmax, float* grad_queries, float* grad_documents,
+                           int64_t n_pairs, int64_t n_queries, int64_t n_documents,
+                           int64_t total_q_tokens, int64_t total_d_tokens, int64_t dim,
+                           int64_t max_q_len, int dtype, void* stream) {
+  (void)n_queries; (void)n_documents;
+  if (!fits_i32(dim) || !fits_i32(max_q_len) || !fits_i32(total_q_tokens) || !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
+  PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
+                             pair_document_ids, n_pairs, dim, max_q_len);
+  return run_backward<kPacked>(t, dscore, argmax, grad_queries, grad_documents, total_q_tokens,
+                               total_d_tokens, 0, dtype, stream);
+}
+
+int maxsim_padded_forward(const void* queries, const int32_t* query_lengths, const void* documents,
+                          const int32_t* doc_lengths, float* scores, int64_t B, int64_t C,
+                          int64_t Lq_max, int64_t Ld_max, int64_t dim, int dtype, void* stream) {
+  if (B < 0 || C < 0 || Lq_max <= 0 || Ld_max <= 0 || !fits_i32(dim) || !fits_i32(Lq_max) ||
+      !fits_i32(Ld_max) || !fits_i32(C))
+    return fail(MAXSIM_EINVAL, "Lq_max/Ld_max/num_candidates must all be > 0");
+  PairTable t = padded_table(queries, query_lengths, documents, doc_lengths, B, C, Lq_max, Ld_max, dim);
+  return run_forward<kPadded, false>(t, scores, nullptr, dtype, stream);
+}
+
+int maxsim_padded_forward_with_argmax(const void* queries, const int32_t* query_lengths,
+                                      const void* documents, const int32_t* doc_lengths,
+                                      float* scores, int32_t* argmax, int64_t B, int64_t C,
+                                      int64_t Lq_max, int64_t Ld_max, int64_t dim, int dtype,
+                                      void* stream) {
+  if (B < 0 || C < 0 || Lq_max <= 0 || Ld_max <= 0 || !fits_i32(dim) || !fits_i32(Lq_max) ||
+      !fits_i32(Ld_max) || !fits_i32(C))
+    return fail(MAXSIM_EINVAL, "Lq_max/Ld_max/num_candidates must all be > 0");
+  PairTable t = padded_table(queries, query_lengths, documents, doc_lengths, B, C, Lq_max, Ld_max, dim);
+  return run_forward<kPadded, true>(t, scores, argmax, dtype, stream);
+}
+
+int maxsim_padded_backward(const float* dscore, const void* queries, const void* documents,
+                           const int32_t* query_lengths, const int32_t* doc_lengths,
+                           const int32_t* argmax, float* grad_queries, float* grad_documents,
+                           int64_t B, int64_t C, int64_t Lq_max, int64_t Ld_max, int64_t dim,
+                           int dtype, void* stream) {
+  if (B < 0 || C < 0 || Lq_max <= 0 || Ld_max <= 0 || !fits_i32(dim) || !fits_i32(Lq_max) ||
+      !fits_i32(Ld_max) || !fits_i32(C))
+    return fail(MAXSIM_EINVAL, "Lq_max/Ld_max/num_candidates must all be > 0");
+  PairTable t = padded_table(queries, query_lengths, documents, doc_lengths, B, C, Lq_max, Ld_max, dim);
+  return run_backward<kPadded>(t, dscore, argmax, grad_queries, grad_documents, B * Lq_max,
+                               B * C * Ld_max, B, dtype, stream);
+}
+
+int maxsim_contrastive_forward(const void* queries, const void* documents,
+                               const int32_t* document_offsets, float* scores, int64_t Nq,
+                               int64_t Lq, int64_t Nb, int64_t dim, int64_t total_d_tokens,
+                               int dtype, void* stream) {
+  if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
+      !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
+  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim);
+  return run_forward<kContrastive, false>(t, scores, nullptr, dtype, stream);
+}
+
+int maxsim_contrastive_forward_with_argmax(const void* queries, const void* documents,
+                                           const int32_t* document_offsets, float* scores,
+                                           int32_t* argmax, int64_t Nq, int64_t Lq, int64_t Nb,
+                                           int64_t dim, int64_t total_d_tokens, int dtype,
+                                           void* stream) {
+  if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
+      !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
+  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim);
+  return run_forward<kContrastive, true>(t, scores, argmax, dtype, stream);
+}
+
+int maxsim_contrastive_backward(const float* dscore, const void* queries, const void* documents,
+                                const int32_t* document_offsets, const int32_t* argmax,
+                                float* grad_queries, float* grad_documents, int64_t Nq, int64_t Lq,
+                                int64_t Nb, int64_t dim, int64_t total_d_tokens, int dtype,
+                                void* stream) {
+  if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
+      !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
+  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim);
+  return run_backward<kContrastive>(t, dscore, argmax, grad_queries, grad_documents, Nq * Lq,
+                                    total_d_tokens, Nq, dtype, stream);
+}
+
+}  // extern "C"
