@@ -1,0 +1,449 @@
+"""Benchmark of the MaxSim hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Headline workload: the large padded rerank configuration (fp16, Nq=256 queries
+of Lq=32, C=1000 candidates each, lognormal document lengths padded to 300,
+dim 128) -- the configuration the pairs/s metric is quoted on.  A step is one
+pass of the padded forward over one such shard.  With N GPUs every rank holds
+its own shard of 256 queries (queries are independent, there is no data-path
+collective), so scaling is weak: the value is all ranks' pairs divided by the
+slowest rank's time.
+
+Printed JSON (one line, rank 0):
+  value      pairs/s with inputs resident in HBM, through the C-ABI operator
+  e2e        pairs/s through the public API from pinned HOST tensors, with the
+             host->device copy of that step's inputs and the device->host read
+             of its scores inside the timed region
+  roofline   algorithmic bytes per launch / measured launch duration, against
+             the measured HBM copy bandwidth
+  cpu_baseline  the reference's PyTorch CPU formulation (einsum + max) timed on
+             the host cores on a bounded sample of the same workload
+  train_step contrastive train-step times (forward + cross-entropy + backward)
+             for the small and the large bf16 contrastive configurations
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+import numpy as np
+import torch
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+METRIC = "scored_pairs_per_s"
+UNIT = "pairs/s"
+WORKLOAD = "c3_padded_rerank_fp16"
+C3 = dict(Nq=256, Lq=32, C=1000, Ld=300, dim=128)
+
+# DRAM bytes per algorithmic byte for the streaming forward kernel, from the
+# ncu capture summarised in profiles/ (dram__bytes_read.sum + write.sum over the
+# algorithmic bytes of the captured launch).  None until a capture exists.
+NCU_TRAFFIC_RATIO = None
+
+
+def _peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                        bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                        source="measured")
+        except Exception:
+            pass
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ---------------------------------------------------------------------------
+# clocks sampling
+# ---------------------------------------------------------------------------
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap,utilization.gpu")
+
+    def __init__(self, device_index: int):
+        self.proc = None
+        self.path = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            ident = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+        except Exception:
+            ident = str(device_index)
+        self.ident = ident
+
+    def start(self):
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.ident}", f"--query-gpu={self.FIELDS}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        rows = []
+        try:
+            for line in open(self.path):
+                parts = [x.strip() for x in line.split(",")]
+                if len(parts) >= 7 and parts[0].isdigit():
+                    rows.append(parts)
+        except Exception:
+            pass
+        finally:
+            try:
+                os.unlink(self.path)
+            except Exception:
+                pass
+        if not rows:
+            return out
+        busy = [r for r in rows if r[6].isdigit() and int(r[6]) >= 50] or rows
+        out["sm_mhz"] = statistics.median(int(r[0]) for r in busy)
+        out["sm_max_mhz"] = max(int(r[1]) for r in rows)
+        out["samples"] = len(busy)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for i, n in enumerate(names):
+            if any(r[2 + i].lower().startswith("active") for r in busy):
+                out["reasons"].append(n)
+        return out
+
+
+# ---------------------------------------------------------------------------
+# CPU baseline (the reference's PyTorch formulation, restated in oracle/)
+# ---------------------------------------------------------------------------
+
+def cpu_padded_baseline(target_seconds: float = 12.0, sample_queries: int = 4, seed: int = 2):
+    """Times einsum+max on the host for a bounded sample of the rerank workload
+    (whole queries with all their C candidates, repeated until about
+    `target_seconds` of CPU work).  Returns (pairs_per_s, cores, sample)."""
+    from maxsim_b200 import workloads as W
+    from oracle import torch_cpu_path as cpu  # baseline leg only
+
+    threads = torch.get_num_threads()
+    wl = W.c3_large_rerank_fp16(seed=seed, Nq=sample_queries,
+                                **{k: C3[k] for k in ("Lq", "C", "Ld", "dim")})
+    q, d = W.to_torch(wl.queries, "fp16"), W.to_torch(wl.documents, "fp16")
+    ql, dl = torch.from_numpy(wl.query_lengths).long(), torch.from_numpy(wl.doc_lengths).long()
+    cpu.padded_scores(q[:1], d[:1], ql[:1], dl[:1], chunk=1)  # warm-up
+    t0 = time.perf_counter()
+    cpu.padded_scores(q, d, ql, dl, chunk=1)
+    once = time.perf_counter() - t0
+    reps = int(max(1, min(50, target_seconds / max(once, 1e-3))))
+    t0 = time.perf_counter()
+    for _ in range(reps):
+        cpu.padded_scores(q, d, ql, dl, chunk=1)
+    dt = time.perf_counter() - t0
+    pairs = sample_queries * C3["C"] * reps
+    return pairs / dt, threads, (f"{sample_queries} queries x {C3['C']} candidates of {WORKLOAD}, "
+                                 f"{reps} passes, {dt:.1f} s")
+
+
+def run_reference_arm(args):
+    """The reference's own CPU path (PyTorch einsum + max) on the host cores.
+    The reference is a Python package whose CPU implementation is its pure
+    PyTorch formulation; it is restated in oracle/torch_cpu_path.py."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from maxsim_b200 import workloads as W
+    from oracle import torch_cpu_path as cpu
+
+    nq = 4
+    wl = W.c3_large_rerank_fp16(seed=2, Nq=nq, **{k: C3[k] for k in ("Lq", "C", "Ld", "dim")})
+    q, d = W.to_torch(wl.queries, "fp16"), W.to_torch(wl.documents, "fp16")
+    ql, dl = torch.from_numpy(wl.query_lengths).long(), torch.from_numpy(wl.doc_lengths).long()
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu.padded_scores(q, d, ql, dl, chunk=1)
+    steps = max(1, min(args.steps, 20))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        cpu.padded_scores(q, d, ql, dl, chunk=1)
+    dt = time.perf_counter() - t0
+    pairs = nq * C3["C"]
+    value = steps * pairs / dt
+    sample = f"{nq} queries x {C3['C']} candidates per step of {WORKLOAD}"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT,
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * dt / steps, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, **C3, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+
+def _event_ms(fn, iters: int):
+    """Per-iteration device times of fn() in ms, CUDA events on the current stream."""
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(iters)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return [a.elapsed_time(b) for a, b in evs]
+
+
+def contrastive_train_step(maxsim, q, d, off, target):
+    q.grad = None
+    d.grad = None
+    s = maxsim.score_contrastive_train(q, d, off)
+    loss = torch.nn.functional.cross_entropy(s, target)
+    loss.backward()
+    return loss
+
+
+def bench_train_steps(dev, peaks, full: bool):
+    """Contrastive train-step times: the 64x64 configuration always, the
+    1024x1024 configuration with ties when `full`."""
+    import maxsim_b200 as maxsim
+    from maxsim_b200 import workloads as W
+
+    out = {}
+    wl = W.c2_contrastive_train_bf16()
+    q = W.to_torch(wl.queries, "bf16", dev).requires_grad_(True)
+    d = W.to_torch(wl.documents, "bf16", dev).requires_grad_(True)
+    off = torch.from_numpy(wl.document_offsets).to(dev)
+    target = torch.arange(q.shape[0], device=dev)
+    flush = torch.empty(256 * 2 ** 20, dtype=torch.uint8, device=dev)
+
+    def step2():
+        flush.zero_()
+        contrastive_train_step(maxsim, q, d, off, target)
+
+    def only_flush():
+        flush.zero_()
+
+    for _ in range(5):
+        step2()
+    t_all = statistics.median(_event_ms(step2, 30))
+    t_flush = statistics.median(_event_ms(only_flush, 30))
+    lens = np.diff(wl.document_offsets).astype(np.int64)
+    flops = 2 * 128 * q.shape[0] * 32 * int(lens.sum()) + 4 * 128 * q.shape[0] * lens.shape[0] * 32
+    out["c2_contrastive_train_bf16"] = {
+        "ms_per_step": t_all - t_flush, "pairs_per_s": q.shape[0] * lens.shape[0] / ((t_all - t_flush) * 1e-3),
+        "tensor_frac": flops / ((t_all - t_flush) * 1e-3) / (peaks["bf16_tflops"] * 1e12),
+        "note": "Nq=Nb=64; L2 flushed between steps (flush time subtracted); launch-latency bound",
+    }
+    if full:
+        data = W.c5_device(dev)
+        q5 = data["queries"].requires_grad_(True)
+        d5 = data["documents"].requires_grad_(True)
+        off5 = data["document_offsets"]
+        t5 = torch.arange(q5.shape[0], device=dev)
+        for _ in range(3):
+            contrastive_train_step(maxsim, q5, d5, off5, t5)
+        ms = statistics.median(_event_ms(lambda: contrastive_train_step(maxsim, q5, d5, off5, t5), 10))
+        with torch.no_grad():
+            fwd = statistics.median(_event_ms(
+                lambda: maxsim._ops.ops.maxsim_contrastive_forward_with_argmax(q5.detach(), d5.detach(), off5), 10))
+        T = int(d5.shape[0])
+        flops = 2 * 128 * 1024 * 32 * T + 4 * 128 * 1024 * 1024 * 32
+        out["c5_contrastive_train_bf16"] = {
+            "ms_per_step": ms, "forward_ms": fwd, "pairs_per_s": 1024 * 1024 / (ms * 1e-3),
+            "tensor_frac": flops / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12),
+            "forward_tensor_frac": (2 * 128 * 1024 * 32 * T) / (fwd * 1e-3) / (peaks["bf16_tflops"] * 1e12),
+            "note": "Nq=Nb=1024, 5% duplicated tokens; step = forward+argmax, cross-entropy, backward",
+        }
+    return out
+
+
+def run_gpu_arm(args):
+    import maxsim_b200 as maxsim
+    from maxsim_b200 import _ops
+    from maxsim_b200 import workloads as W
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (there is no CPU path)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist_mod
+        dist = dist_mod
+        dist.init_process_group("nccl", device_id=dev)
+    peaks = _peaks()
+
+    Nq, Lq, C, Ld, dim = (C3[k] for k in ("Nq", "Lq", "C", "Ld", "dim"))
+    if args.small:
+        Nq = 16
+    q_begin = rank * Nq
+    data = W.c3_device_shard(q_begin, q_begin + Nq, dev, Lq=Lq, C=C, Ld=Ld, dim=dim)
+    queries, documents = data["queries"], data["documents"]
+    qlen, dlen = data["query_lengths"], data["doc_lengths"]
+    q_flat = queries.view(Nq * Lq, dim)
+    d_flat = documents.view(Nq * C * Ld, dim)
+    dlen_flat = dlen.view(-1).contiguous()
+    pairs = Nq * C
+    valid_doc_tokens = int(dlen.sum().item())
+    valid_q_tokens = int(qlen.sum().item())
+    algo_bytes = (valid_doc_tokens + valid_q_tokens) * dim * 2 + 4 * pairs
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+
+    def step():
+        return _ops.ops.maxsim_padded_forward(q_flat, qlen, d_flat, dlen_flat, Lq, Ld, C)
+
+    # --- device-resident throughput -----------------------------------------
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    launches0 = _ops.launch_count()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    t0.record()
+    for _ in range(args.steps):
+        scores = step()
+    t1.record()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    launches = _ops.launch_count() - launches0
+    elapsed_ms = t0.elapsed_time(t1)
+    # per-launch durations for the roofline, same stream, same region shape
+    launch_ms = _event_ms(step, min(args.steps, 20))
+    kernel_ms = statistics.mean(launch_ms)
+
+    # --- end to end from host memory through the public API -----------------
+    e2e_steps = max(1, min(args.steps, 3))
+    hq = torch.empty(queries.shape, dtype=queries.dtype, pin_memory=True).copy_(queries)
+    hd = torch.empty(documents.shape, dtype=documents.dtype, pin_memory=True)
+    hd.copy_(documents)
+    hql = qlen.cpu().pin_memory()
+    hdl = dlen.cpu().pin_memory()
+    h_scores = torch.empty((Nq, C), dtype=torch.float32, pin_memory=True)
+
+    def e2e_step():
+        dq = queries.copy_(hq, non_blocking=True)
+        dd = documents.copy_(hd, non_blocking=True)
+        dql = qlen.copy_(hql, non_blocking=True)
+        ddl = dlen.copy_(hdl, non_blocking=True)
+        s = maxsim.score_candidates_padded(dq, dd, dql, ddl)
+        h_scores.copy_(s, non_blocking=True)
+
+    e2e_step()
+    torch.cuda.synchronize()
+    if dist:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    h2d = hq.numel() * 2 + hd.numel() * 2 + hql.numel() * 4 + hdl.numel() * 4
+    d2h = h_scores.numel() * 4
+    del hd
+
+    # keep the kernel running long enough for the clock sampler to see it
+    t_end = time.time() + 1.5
+    while time.time() < t_end:
+        for _ in range(10):
+            step()
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    status = _ops.device_status()
+
+    # --- max over ranks ------------------------------------------------------
+    times = torch.tensor([elapsed_ms, e2e_ms, kernel_ms], dtype=torch.float64, device=dev)
+    if dist:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    elapsed_ms, e2e_ms, kernel_ms = (float(x) for x in times.tolist())
+
+    train = None
+    cpu_base = None
+    if rank == 0 and world == 1:
+        del documents, d_flat, data
+        torch.cuda.empty_cache()
+        train = bench_train_steps(dev, peaks, full=not args.small)
+        v, cores, sample = cpu_padded_baseline(target_seconds=2.0 if args.small else 12.0)
+        cpu_base = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        value = world * pairs * args.steps / (elapsed_ms * 1e-3)
+        achieved = algo_bytes / (kernel_ms * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "per_gpu": dict(Nq=Nq, Lq=Lq, C=C, Ld=Ld, dim=dim),
+                       "pairs_per_gpu": pairs, "valid_doc_tokens_per_gpu": valid_doc_tokens,
+                       "parallelism": f"query-sharded x{world}, no collective",
+                       "l2": "inputs (19.7 GB padded, 12.3 GB valid) are larger than L2"},
+            "e2e": {"value": world * pairs * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
+                         "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                         "peak_source": peaks["source"], "kernel_ms": kernel_ms,
+                         "algorithmic_bytes": algo_bytes,
+                         "traffic": (None if NCU_TRAFFIC_RATIO is None
+                                     else NCU_TRAFFIC_RATIO * algo_bytes)},
+            "clocks": clocks,
+            "device_status": status,
+        }
+        if cpu_base is not None:
+            line["cpu_baseline"] = cpu_base
+        if train is not None:
+            line["train_step"] = train
+        print(json.dumps(line), flush=True)
+    if dist:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="maxsim_b200", choices=["maxsim_b200", "reference"])
+    ap.add_argument("--small", action="store_true",
+                    help="16 queries per GPU instead of 256 (for profiler captures; not a bench value)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -40,6 +40,13 @@ __all__ = [
 
 __version__ = "0.1.0"
 
+# The operators call into the library through ctypes, which a tracing compiler
+# cannot see through.  Marking the public functions keeps them out of
+# torch.compile graphs: a compiled caller breaks the graph around them and runs
+# them eagerly, as the reference's tests require (tests/test_compat.py:111-152,
+# fullgraph=False).
+_eager = torch.compiler.disable
+
 
 # ---------------------------------------------------------------------------
 # Packed pair grids (torch-ext/maxsim/__init__.py:226-508)
@@ -54,6 +61,7 @@ def _packed_prologue(queries, query_offsets, documents, document_offsets,
     return _v.resolve_max_q_len(max_q_len, actual)
 
 
+@_eager
 def score_pairs_packed(queries, query_offsets, documents, document_offsets,
                        pair_query_ids, pair_document_ids, *,
                        max_q_len: Optional[int] = None) -> torch.Tensor:
@@ -71,6 +79,7 @@ def score_pairs_packed(queries, query_offsets, documents, document_offsets,
                               pair_query_ids.contiguous(), pair_document_ids.contiguous(), mql)
 
 
+@_eager
 def score_pairs_packed_with_argmax(queries, query_offsets, documents, document_offsets,
                                    pair_query_ids, pair_document_ids, *,
                                    max_q_len: Optional[int] = None
@@ -109,6 +118,7 @@ class _PackedFn(torch.autograd.Function):
         return dq, None, dd, None, None, None, None
 
 
+@_eager
 def score_pairs_packed_train(queries, query_offsets, documents, document_offsets,
                              pair_query_ids, pair_document_ids, *,
                              max_q_len: Optional[int] = None) -> torch.Tensor:
@@ -130,6 +140,7 @@ def _flatten_padded(queries, documents, query_lengths, doc_lengths, B, C, Lq, Ld
             doc_lengths.reshape(B * C).to(dtype=torch.int32).contiguous())
 
 
+@_eager
 def score_candidates_padded(queries, documents, query_lengths, doc_lengths) -> torch.Tensor:
     """``[B, C]`` fp32 scores of ``queries [B, Lq, D]`` against
     ``documents [B, C, Ld, D]``; only the first ``query_lengths[b]`` /
@@ -140,6 +151,7 @@ def score_candidates_padded(queries, documents, query_lengths, doc_lengths) -> t
     return ops.maxsim_padded_forward(q, qlen, d, dlen, int(Lq), int(Ld), int(C)).view(B, C)
 
 
+@_eager
 def score_candidates_padded_with_argmax(queries, documents, query_lengths, doc_lengths
                                         ) -> Tuple[torch.Tensor, torch.Tensor]:
     """As :func:`score_candidates_padded`, plus ``argmax [B, C, Lq]`` int32
@@ -176,6 +188,7 @@ class _PaddedFn(torch.autograd.Function):
         return dq.view(B, Lq, D), dd.view(B, C, Ld, D), None, None
 
 
+@_eager
 def score_candidates_padded_train(queries, documents, query_lengths, doc_lengths) -> torch.Tensor:
     """Differentiable :func:`score_candidates_padded`."""
     _v.check_padded(queries, documents, query_lengths, doc_lengths)
@@ -186,6 +199,7 @@ def score_candidates_padded_train(queries, documents, query_lengths, doc_lengths
 # Contrastive all-pairs (torch-ext/maxsim/__init__.py:880-979)
 # ---------------------------------------------------------------------------
 
+@_eager
 def score_contrastive(queries, documents, document_offsets) -> torch.Tensor:
     """``[Nq, Nb]`` fp32 scores of every query ``[Nq, Lq, D]`` against every
     packed document (``documents [total_d_tokens, D]``, ``document_offsets [Nb+1]``)."""
@@ -195,6 +209,7 @@ def score_contrastive(queries, documents, document_offsets) -> torch.Tensor:
         document_offsets.to(dtype=torch.int32).contiguous())
 
 
+@_eager
 def score_contrastive_with_argmax(queries, documents, document_offsets
                                   ) -> Tuple[torch.Tensor, torch.Tensor]:
     """As :func:`score_contrastive`, plus ``argmax [Nq, Nb, Lq]`` int32."""
@@ -224,6 +239,7 @@ class _ContrastiveFn(torch.autograd.Function):
         return dq, dd, None
 
 
+@_eager
 def score_contrastive_train(queries, documents, document_offsets) -> torch.Tensor:
     """Differentiable :func:`score_contrastive`."""
     _v.check_contrastive(queries, documents, document_offsets)

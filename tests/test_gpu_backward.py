@@ -1,0 +1,188 @@
+"""Backward parity on the GPU (reference: tests/test_backward.py,
+test_contrastive.py:98-167, test_packed_train.py, test_edge_shapes.py:74-116).
+
+Gradients are compared with the oracle's routing through the argmax the kernel
+itself produced, which keeps the check meaningful where a near-tie lets the
+argmax legitimately differ; the argmax itself is checked against the oracle in
+the forward tests."""
+
+from __future__ import annotations
+
+import numpy as np
+import pytest
+import torch
+
+import maxsim_b200 as maxsim
+from maxsim_b200 import _ops
+from _util import NAME_OF, assert_grads, f32, i64, oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert _ops.device_status() == 0
+
+
+PADDED = [(1, 1, 16, 16, 16), (1, 1, 16, 17, 16), (1, 1, 16, 32, 16), (1, 1, 16, 64, 16),
+          (1, 1, 32, 1, 16), (4, 1, 16, 33, 64), (1, 8, 32, 50, 64), (3, 7, 32, 120, 128),
+          (2, 3, 9, 20, 24), (2, 2, 40, 70, 96)]
+
+
+@pytest.mark.parametrize("B,C,Lq,Ld,dim", PADDED)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_padded_backward(B, C, Lq, Ld, dim, dtype):
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(B, Lq, dim, generator=g).to(DEV, dtype).requires_grad_(True)
+    d = torch.randn(B, C, Ld, dim, generator=g).to(DEV, dtype).requires_grad_(True)
+    qlen = torch.randint(1, Lq + 1, (B,), generator=g, dtype=torch.int32).to(DEV)
+    dlen = torch.randint(1, Ld + 1, (B, C), generator=g, dtype=torch.int32).to(DEV)
+    w = torch.randn(B, C, generator=g).to(DEV)
+    scores = maxsim.score_candidates_padded_train(q, d, qlen, dlen)
+    (scores * w).sum().backward()
+    assert q.grad.dtype == dtype and d.grad.dtype == dtype
+    _, a = maxsim.score_candidates_padded_with_argmax(q.detach(), d.detach(), qlen, dlen)
+    # the op-level gradients are fp32; compare those
+    dq, dd = _ops.ops.maxsim_padded_backward(
+        w.reshape(-1), q.detach().reshape(B * Lq, dim), d.detach().reshape(B * C * Ld, dim),
+        qlen, dlen.reshape(-1), a.reshape(B * C, Lq), Lq, Ld, C)
+    assert dq.dtype == torch.float32 and dd.dtype == torch.float32
+    wq, wd = oracle.candidates_padded_backward(f32(w), f32(q), f32(d), i64(qlen), i64(dlen),
+                                               a.cpu().numpy())
+    name = NAME_OF[dtype]
+    assert_grads(f32(dq).reshape(wq.shape), wq, name, "grad_queries")
+    assert_grads(f32(dd).reshape(wd.shape), wd, name, "grad_documents")
+    assert_grads(f32(q.grad), wq, "bf16" if dtype != torch.float32 else "fp32", "queries.grad")
+    # rows past the lengths receive exactly zero
+    for b in range(B):
+        assert (dq.view(B, Lq, dim)[b, int(qlen[b]):] == 0).all()
+        for c in range(C):
+            assert (dd.view(B, C, Ld, dim)[b, c, int(dlen[b, c]):] == 0).all()
+
+
+CONTRASTIVE = [(1, 16, [16], 16), (2, 16, [7, 8, 100], 32), (4, 32, [50, 50, 50, 50], 128),
+               (6, 32, [1, 65, 64, 130, 300], 128), (3, 20, [33, 5], 96), (5, 32, [70] * 9, 64)]
+
+
+@pytest.mark.parametrize("Nq,Lq,d_lens,dim", CONTRASTIVE)
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_contrastive_backward(Nq, Lq, d_lens, dim, dtype):
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(Nq, Lq, dim, generator=g).to(DEV, dtype).requires_grad_(True)
+    d = torch.randn(sum(d_lens), dim, generator=g).to(DEV, dtype).requires_grad_(True)
+    off = torch.zeros(len(d_lens) + 1, dtype=torch.int32)
+    off[1:] = torch.tensor(d_lens, dtype=torch.int32).cumsum(0)
+    off = off.to(DEV)
+    w = torch.randn(Nq, len(d_lens), generator=g).to(DEV)
+    scores = maxsim.score_contrastive_train(q, d, off)
+    (scores * w).sum().backward()
+    _, a = maxsim.score_contrastive_with_argmax(q.detach(), d.detach(), off)
+    dq, dd = _ops.ops.maxsim_contrastive_backward(w, q.detach(), d.detach(), off, a)
+    wq, wd = oracle.contrastive_backward(f32(w), f32(q), f32(d), i64(off), a.cpu().numpy())
+    name = NAME_OF[dtype]
+    assert_grads(f32(dq), wq, name, "grad_queries")
+    assert_grads(f32(dd), wd, name, "grad_documents")
+    assert q.grad is not None and d.grad is not None
+    assert_grads(f32(d.grad), wd, "bf16" if dtype != torch.float32 else "fp32", "documents.grad")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_packed_backward_with_duplicate_pairs(dtype):
+    g = torch.Generator().manual_seed(2)
+    q_lens, d_lens, dim = [8, 32, 17, 9], [8, 200, 33, 120, 64], 96
+    q = torch.randn(sum(q_lens), dim, generator=g).to(DEV, dtype).requires_grad_(True)
+    d = torch.randn(sum(d_lens), dim, generator=g).to(DEV, dtype).requires_grad_(True)
+    qoff = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device=DEV)
+    doff = torch.tensor(np.concatenate([[0], np.cumsum(d_lens)]), dtype=torch.int32, device=DEV)
+    pq = torch.tensor([0, 1, 1, 2, 3, 1, 0, 1], dtype=torch.int32, device=DEV)
+    pd = torch.tensor([0, 1, 1, 4, 2, 3, 0, 1], dtype=torch.int32, device=DEV)  # (1,1) x3, (0,0) x2
+    w = torch.randn(pq.shape[0], generator=g).to(DEV)
+    scores = maxsim.score_pairs_packed_train(q, qoff, d, doff, pq, pd)
+    (scores * w).sum().backward()
+    s2, a = maxsim.score_pairs_packed_with_argmax(q.detach(), qoff, d.detach(), doff, pq, pd)
+    assert torch.equal(scores.detach(), s2)
+    dq, dd = _ops.ops.maxsim_packed_backward(w, q.detach(), qoff, d.detach(), doff, pq, pd, a,
+                                             a.shape[1])
+    wq, wd = oracle.pairs_packed_backward(f32(w), f32(q), i64(qoff), f32(d), i64(doff), i64(pq),
+                                          i64(pd), a.cpu().numpy())
+    name = NAME_OF[dtype]
+    assert_grads(f32(dq), wq, name, "grad_queries")
+    assert_grads(f32(dd), wd, name, "grad_documents")
+
+
+@pytest.mark.parametrize("api", ["padded", "contrastive", "packed"])
+def test_zero_upstream_gradient_gives_exact_zeros(api):
+    dt = torch.float16
+    if api == "padded":
+        q = torch.randn(2, 16, 64, device=DEV, dtype=dt, requires_grad=True)
+        d = torch.randn(2, 3, 40, 64, device=DEV, dtype=dt, requires_grad=True)
+        qlen = torch.full((2,), 16, dtype=torch.int32, device=DEV)
+        dlen = torch.full((2, 3), 40, dtype=torch.int32, device=DEV)
+        s = maxsim.score_candidates_padded_train(q, d, qlen, dlen)
+    elif api == "contrastive":
+        q = torch.randn(3, 16, 64, device=DEV, dtype=dt, requires_grad=True)
+        d = torch.randn(100, 64, device=DEV, dtype=dt, requires_grad=True)
+        off = torch.tensor([0, 30, 100], dtype=torch.int32, device=DEV)
+        s = maxsim.score_contrastive_train(q, d, off)
+    else:
+        q = torch.randn(20, 64, device=DEV, dtype=dt, requires_grad=True)
+        d = torch.randn(50, 64, device=DEV, dtype=dt, requires_grad=True)
+        qoff = torch.tensor([0, 8, 20], dtype=torch.int32, device=DEV)
+        doff = torch.tensor([0, 25, 50], dtype=torch.int32, device=DEV)
+        ids = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+        s = maxsim.score_pairs_packed_train(q, qoff, d, doff, ids, ids)
+    (s * 0.0).sum().backward()
+    assert (q.grad == 0).all() and (d.grad == 0).all()
+
+
+def test_autocast_compile_and_stability():
+    dt = torch.bfloat16
+    q = torch.randn(4, 16, 64, device=DEV, dtype=dt, requires_grad=True)
+    d = torch.randn(128, 64, device=DEV, dtype=dt, requires_grad=True)
+    off = torch.arange(0, 160, 32, dtype=torch.int32, device=DEV)
+    with torch.autocast(device_type="cuda", dtype=dt):
+        loss = maxsim.score_contrastive_train(q, d, off).sum()
+    loss.backward()
+    assert torch.isfinite(loss) and torch.isfinite(q.grad).all() and torch.isfinite(d.grad).all()
+
+    def step(q, d):
+        return maxsim.score_contrastive_train(q, d, off).sum()
+
+    eager = step(q.detach(), d.detach())
+    out = torch.compile(step, fullgraph=False)(q.detach(), d.detach())
+    torch.testing.assert_close(out, eager, rtol=1e-3, atol=1e-3)
+
+    torch.cuda.synchronize()
+    base = torch.cuda.memory_allocated()
+    for _ in range(100):
+        q.grad = None
+        d.grad = None
+        maxsim.score_contrastive_train(q, d, off).sum().backward()
+    torch.cuda.synchronize()
+    assert torch.cuda.memory_allocated() - base < 20 * 2 ** 20
+    assert torch.isfinite(q.grad).all()
+
+
+def test_training_reduces_contrastive_loss():
+    """In-batch InfoNCE on the contrastive op converges (reference:
+    tests/test_train_convergence.py:90-112)."""
+    torch.manual_seed(0)
+    Nq, Lq, Ld, D = 16, 16, 24, 64
+    q = torch.nn.Parameter(torch.randn(Nq, Lq, D, device=DEV) * 0.5)
+    d = torch.nn.Parameter(torch.randn(Nq * Ld, D, device=DEV) * 0.5)
+    off = torch.arange(0, (Nq + 1) * Ld, Ld, dtype=torch.int32, device=DEV)
+    opt = torch.optim.Adam([q, d], lr=5e-2)
+    target = torch.arange(Nq, device=DEV)
+    losses = []
+    for _ in range(50):
+        opt.zero_grad()
+        qn = torch.nn.functional.normalize(q, dim=-1).half()
+        dn = torch.nn.functional.normalize(d, dim=-1).half()
+        s = maxsim.score_contrastive_train(qn, dn, off)
+        loss = torch.nn.functional.cross_entropy(s / 0.5, target)
+        loss.backward()
+        opt.step()
+        losses.append(float(loss))
+    assert losses[-1] < 0.7 * losses[0], losses[::10]
