@@ -325,20 +325,30 @@ def run_gpu_arm(args):
     if dist:
         dist.barrier()
     launches0 = _ops.launch_count()
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps + 1)]
     torch.cuda.synchronize()
-    t0.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
+        marks[i].record()
         scores = step()
-    t1.record()
+    marks[args.steps].record()
     torch.cuda.synchronize()
     if dist:
         dist.barrier()
     launches = _ops.launch_count() - launches0
-    elapsed_ms = t0.elapsed_time(t1)
-    # per-launch durations for the roofline, same stream, same region shape
-    launch_ms = _event_ms(step, min(args.steps, 20))
+    elapsed_ms = marks[0].elapsed_time(marks[args.steps])
+    # per-launch durations for the roofline: the same launches, same stream
+    launch_ms = [marks[i].elapsed_time(marks[i + 1]) for i in range(args.steps)]
     kernel_ms = statistics.mean(launch_ms)
+
+    if args.kernel_only:
+        sampler.stop()
+        if rank == 0:
+            print(json.dumps({"profile_run": True, "workload": WORKLOAD, "pairs": pairs,
+                              "algorithmic_bytes": algo_bytes, "kernel_ms": kernel_ms,
+                              "ms_per_step": elapsed_ms / args.steps}), flush=True)
+        if dist:
+            dist.destroy_process_group()
+        return
 
     # --- end to end from host memory through the public API -----------------
     e2e_steps = max(1, min(args.steps, 3))
@@ -438,6 +448,8 @@ def main():
     ap.add_argument("--impl", default="maxsim_b200", choices=["maxsim_b200", "reference"])
     ap.add_argument("--small", action="store_true",
                     help="16 queries per GPU instead of 256 (for profiler captures; not a bench value)")
+    ap.add_argument("--kernel-only", action="store_true",
+                    help="run only the device-resident loop (for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

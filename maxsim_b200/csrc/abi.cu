@@ -119,6 +119,10 @@ bool mma_eligible(const PairTable& t, int dtype) {
   if (!(t.dim == 32 || t.dim == 64 || t.dim == 96 || t.dim == 128)) return false;
   if (!aligned16(t.queries) || !aligned16(t.documents)) return false;
   if (t.n_pairs >= (1ll << 31)) return false;
+  if (t.q_slots > 32767) return false;
+  // the streaming kernel indexes token rows with 32 bits
+  if (t.Ld_max > 0 && t.n_pairs * (int64_t)t.Ld_max >= (1ll << 31)) return false;
+  if ((t.n_pairs / t.C + 1) * (int64_t)t.q_slots >= (1ll << 31)) return false;
   return true;
 }
 

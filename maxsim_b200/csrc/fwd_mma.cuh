@@ -4,13 +4,13 @@
 // they are bound by how fast document tokens stream out of HBM.  This kernel
 // is built around that stream:
 //
-//   * persistent CTAs, one per SM, eight warps each; every warp owns whole
+//   * persistent CTAs, one per SM, twelve warps each; every warp owns whole
 //     (query, document) pairs, so no cross-warp reduction exists;
 //   * each warp keeps its own ring of kStages shared-memory slots of 16
 //     document tokens.  Lane 0 feeds the ring with TMA bulk copies
 //     (cp.async.bulk global -> shared, completion on an mbarrier), running
 //     kStages tiles ahead of the math and straight across pair boundaries, so
-//     the memory system always has eight rings per SM in flight;
+//     the memory system always has twelve rings per SM in flight;
 //   * padding rows are never fetched: the last tile of a document copies only
 //     its valid tokens;
 //   * the query (<= 32 rows per pass) lives in registers as mma.sync A
@@ -30,10 +30,10 @@
 
 namespace maxsim {
 
-constexpr int kMmaWarps = 8;
+constexpr int kMmaWarps = 12;
 constexpr int kMmaThreads = kMmaWarps * 32;
 constexpr int kTileTokens = 16;
-constexpr int kStages = 6;
+constexpr int kStages = 4;
 constexpr uint32_t kSpinLimit = 1u << 24;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -108,22 +108,59 @@ __device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
 }
 
 // What lane 0 records for the math side about the tile it put in a slot.
-struct __align__(16) TileMeta {
-  int32_t pair;     // -1: no more work
-  int32_t j0;       // first document token of the tile
+// Record A is read for every tile, record B only for the first tile of a
+// (pair, query pass).
+struct __align__(16) TileMetaA {
+  int32_t pair;   // -1: no more work
+  int32_t j0;     // first document token of the tile
   int32_t Ld;
-  int32_t Lq;
-  int32_t q_row_lo; // first query row of this pass (64-bit split)
-  int32_t q_row_hi;
-  int32_t q0;       // query-row offset of this pass within the pair
-  int32_t pad;
+  int32_t lq_q0;  // Lq | (q0 << 16): query length and row offset of this pass
 };
+struct __align__(16) TileMetaB {
+  int32_t q_row;  // first query row of this pass
+  int32_t pad0, pad1, pad2;
+};
+
+struct Geo32 {
+  int32_t q_row0, d_row0, Lq, Ld;
+};
+
+// Pair geometry with 32-bit rows (the dispatcher guarantees every row index
+// and pair index fits).
+template <int LAYOUT>
+__device__ __forceinline__ Geo32 geo32(const PairTable& t, int32_t p) {
+  Geo32 g;
+  if constexpr (LAYOUT == kPadded) {
+    const int32_t b = (int32_t)((uint32_t)p / (uint32_t)t.C);
+    g.q_row0 = b * t.q_slots;
+    g.Lq = __ldg(t.ia + b);
+    g.d_row0 = p * t.Ld_max;
+    g.Ld = __ldg(t.ib + p);
+  } else if constexpr (LAYOUT == kPacked) {
+    const int32_t qi = __ldg(t.ic + p);
+    const int32_t di = __ldg(t.id + p);
+    g.q_row0 = __ldg(t.ia + qi);
+    g.Lq = __ldg(t.ia + qi + 1) - g.q_row0;
+    g.d_row0 = __ldg(t.ib + di);
+    g.Ld = __ldg(t.ib + di + 1) - g.d_row0;
+  } else {
+    const int32_t qi = (int32_t)((uint32_t)p / (uint32_t)t.C);
+    const int32_t di = p - qi * t.C;
+    g.q_row0 = qi * t.q_slots;
+    g.Lq = t.q_slots;
+    g.d_row0 = __ldg(t.ib + di);
+    g.Ld = __ldg(t.ib + di + 1) - g.d_row0;
+  }
+  g.Lq = max(0, min(g.Lq, t.q_slots));
+  g.Ld = max(0, g.Ld);
+  return g;
+}
 
 template <int DIM>
 constexpr size_t mma_smem_bytes() {
-  return (size_t)kMmaWarps * kStages * (kTileTokens * DIM * 2)  // rings
-         + (size_t)kMmaWarps * kStages * sizeof(TileMeta)         // tile records
-         + (size_t)kMmaWarps * kStages * 8;                       // mbarriers
+  return (size_t)kMmaWarps * kStages * (kTileTokens * DIM * 2)                        // rings
+         + (size_t)kMmaWarps * kStages * (sizeof(TileMetaA) + sizeof(TileMetaB))      // records
+         + (size_t)kMmaWarps * kStages * 8;                                           // mbarriers
 }
 
 template <typename T, int DIM, int LAYOUT, bool ARGMAX>
@@ -139,10 +176,14 @@ fwd_mma_kernel(PairTable t, float* __restrict__ scores, int32_t* __restrict__ ar
   const int g = lane >> 2, tq = lane & 3;
 
   unsigned char* ring = mma_smem + (size_t)warp * kStages * kStageBytes;
-  TileMeta* metas = reinterpret_cast<TileMeta*>(mma_smem + (size_t)kMmaWarps * kStages * kStageBytes) +
-                    warp * kStages;
+  unsigned char* after_rings = mma_smem + (size_t)kMmaWarps * kStages * kStageBytes;
+  TileMetaA* metaA = reinterpret_cast<TileMetaA*>(after_rings) + warp * kStages;
+  TileMetaB* metaB =
+      reinterpret_cast<TileMetaB*>(after_rings + (size_t)kMmaWarps * kStages * sizeof(TileMetaA)) +
+      warp * kStages;
   uint64_t* bars = reinterpret_cast<uint64_t*>(
-                       mma_smem + (size_t)kMmaWarps * kStages * (kStageBytes + sizeof(TileMeta))) +
+                       after_rings +
+                       (size_t)kMmaWarps * kStages * (sizeof(TileMetaA) + sizeof(TileMetaB))) +
                    warp * kStages;
   const uint32_t ring_u32 = smem_u32(ring);
   const uint32_t bars_u32 = smem_u32(bars);
@@ -155,73 +196,74 @@ fwd_mma_kernel(PairTable t, float* __restrict__ scores, int32_t* __restrict__ ar
   __syncwarp();
 
   // ---- feeding cursor (uniform across the warp) ---------------------------
-  const int64_t n_chunks = (t.n_pairs + pairs_per_chunk - 1) / pairs_per_chunk;
-  // consecutive chunks go to different SMs first, then to different warps
-  const int64_t warp_global = (int64_t)warp * gridDim.x + blockIdx.x;
-  const int64_t warps_total = (int64_t)gridDim.x * kMmaWarps;
-  int64_t chunk = warp_global;
-  int64_t fp = 0, fp_end = 0;  // current pair, end of current chunk
-  bool f_done = chunk >= n_chunks;
-  PairGeom fg;
-  fg.q_row0 = 0; fg.d_row0 = 0; fg.Lq = 0; fg.Ld = 0;
+  // Chunks of `pairs_per_chunk` consecutive pairs are dealt round-robin:
+  // consecutive chunks go to different SMs first, then to different warps.
+  const int32_t n_pairs = (int32_t)t.n_pairs;
+  const int32_t n_chunks = (n_pairs + pairs_per_chunk - 1) / pairs_per_chunk;
+  const int32_t warps_total = (int32_t)gridDim.x * kMmaWarps;
+  int32_t f_chunk = warp * (int32_t)gridDim.x + (int32_t)blockIdx.x;  // chunk of the NEXT pair
+  int32_t fp = -1;     // pair being fed (-1: none left)
+  int32_t np = -1;     // the pair after it, geometry already requested
+  int32_t np_end = 0;  // end of np's chunk
+  Geo32 cur, nxt;
+  cur.q_row0 = cur.d_row0 = cur.Lq = cur.Ld = 0;
+  nxt = cur;
   int f_q0 = 0, f_j0 = 0;
-  if (!f_done) {
-    fp = chunk * pairs_per_chunk;
-    fp_end = min(fp + (int64_t)pairs_per_chunk, t.n_pairs);
-    fg = pair_geom<LAYOUT>(t, fp);
-  }
+
+  auto fetch_next = [&]() {  // np <- successor of np within this warp's chunks; request its geometry
+    if (np >= 0 && np + 1 < np_end) {
+      ++np;
+    } else if (f_chunk < n_chunks) {
+      np = f_chunk * pairs_per_chunk;
+      np_end = min(np + pairs_per_chunk, n_pairs);
+      f_chunk += warps_total;
+    } else {
+      np = -1;
+    }
+    if (np >= 0) nxt = geo32<LAYOUT>(t, np);
+  };
+  auto next_pair = [&]() {
+    fp = np;
+    cur = nxt;
+    if (np >= 0) fetch_next();
+  };
+  fetch_next();
+  next_pair();
+
   const unsigned char* dbase = reinterpret_cast<const unsigned char*>(t.documents);
   const unsigned char* qbase = reinterpret_cast<const unsigned char*>(t.queries);
 
   auto feed = [&](int s) {
-    if (f_done) {
-      if (lane == 0) metas[s].pair = -1;
+    if (fp < 0) {
+      if (lane == 0) metaA[s].pair = -1;
       return;
     }
-    const int n_valid = max(0, min(kTileTokens, fg.Ld - f_j0));
+    const int n_valid = max(0, min(kTileTokens, cur.Ld - f_j0));
     if (lane == 0) {
-      TileMeta m;
-      m.pair = (int32_t)fp;
-      m.j0 = f_j0;
-      m.Ld = fg.Ld;
-      m.Lq = fg.Lq;
-      const int64_t qrow = fg.q_row0 + f_q0;
-      m.q_row_lo = (int32_t)(qrow & 0xffffffffll);
-      m.q_row_hi = (int32_t)(qrow >> 32);
-      m.q0 = f_q0;
-      m.pad = 0;
-      metas[s] = m;
+      TileMetaA a;
+      a.pair = fp;
+      a.j0 = f_j0;
+      a.Ld = cur.Ld;
+      a.lq_q0 = cur.Lq | (f_q0 << 16);
+      metaA[s] = a;
+      if (f_j0 == 0) metaB[s].q_row = cur.q_row0 + f_q0;
       const uint32_t bytes = (uint32_t)n_valid * kRowBytes;
       mbar_expect_tx(bars_u32 + 8 * s, bytes);
       if (bytes) {
         bulk_g2s(ring_u32 + s * kStageBytes,
-                 dbase + (fg.d_row0 + f_j0) * (int64_t)kRowBytes, bytes, bars_u32 + 8 * s);
+                 dbase + (int64_t)(cur.d_row0 + f_j0) * kRowBytes, bytes, bars_u32 + 8 * s);
       }
     }
-    // advance: next tile, next query pass, next pair, next chunk
     f_j0 += kTileTokens;
-    if (f_j0 >= fg.Ld) {
+    if (f_j0 >= cur.Ld) {
       f_j0 = 0;
       f_q0 += 32;
-      if (f_q0 >= fg.Lq) {
+      if (f_q0 >= cur.Lq) {
         f_q0 = 0;
-        ++fp;
-        if (fp >= fp_end) {
-          chunk += warps_total;
-          if (chunk >= n_chunks) {
-            f_done = true;
-          } else {
-            fp = chunk * pairs_per_chunk;
-            fp_end = min(fp + (int64_t)pairs_per_chunk, t.n_pairs);
-          }
-        }
-        if (!f_done) fg = pair_geom<LAYOUT>(t, fp);
+        next_pair();
       }
     }
   };
-
-  for (int s = 0; s < kStages; ++s) feed(s);
-  __syncwarp();
 
   // ---- math side ----------------------------------------------------------
   uint32_t afrag[2][DIM / 16][4];
@@ -231,139 +273,173 @@ fwd_mma_kernel(PairTable t, float* __restrict__ scores, int32_t* __restrict__ ar
     for (int ks = 0; ks < DIM / 16; ++ks)
 #pragma unroll
       for (int r = 0; r < 4; ++r) afrag[mt][ks][r] = 0u;
-  int64_t a_row = -1;  // query row the fragments were loaded from
+  int32_t a_row = -1;  // query row the fragments were loaded from
   int a_rows = 0;      // valid rows in the fragments
 
   float run[2][2];
   int idx[2][2];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) { run[mt][h] = neg_inf(); idx[mt][h] = 0; }
   float score_acc = 0.0f;
 
   int s = 0;
   uint32_t parity = 0;
-  for (;; ++s) {
-    if (s == kStages) { s = 0; parity ^= 1u; }
-    const TileMeta m = metas[s];
-    if (m.pair < 0) break;
-    const int rows = min(32, m.Lq - m.q0);
+  for (int it = 0;; ++it, ++s) {
+    if (s == kStages) { s = 0; if (it > kStages) parity ^= 1u; }
+    if (it >= kStages) {
+      const TileMetaA m = metaA[s];
+      if (m.pair < 0) break;
+      const int j0 = m.j0, Ld = m.Ld;
+      const int Lq = m.lq_q0 & 0xffff, q0 = m.lq_q0 >> 16;
 
-    if (m.j0 == 0) {
-      const int64_t qrow = ((int64_t)m.q_row_hi << 32) | (uint32_t)m.q_row_lo;
-      if (qrow != a_row || rows != a_rows) {
-        a_row = qrow;
-        a_rows = rows;
-        const unsigned char* qp = qbase + qrow * (int64_t)kRowBytes + tq * 16;
+      if (j0 == 0) {
+        const int32_t qrow = metaB[s].q_row;
+        const int rows = min(32, Lq - q0);
+        if (qrow != a_row || rows != a_rows) {
+          a_row = qrow;
+          a_rows = rows;
+          const unsigned char* qp = qbase + (int64_t)qrow * kRowBytes + tq * 16;
 #pragma unroll
-        for (int mt = 0; mt < 2; ++mt) {
-          const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
+          for (int mt = 0; mt < 2; ++mt) {
+            const int r_lo = mt * 16 + g, r_hi = r_lo + 8;
 #pragma unroll
-          for (int c = 0; c < kChunks; ++c) {
-            uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
-            if (r_lo < rows) lo = ldg_nc_v4(qp + (int64_t)r_lo * kRowBytes + c * 64);
-            if (r_hi < rows) hi = ldg_nc_v4(qp + (int64_t)r_hi * kRowBytes + c * 64);
-            afrag[mt][2 * c][0] = lo.x; afrag[mt][2 * c][1] = hi.x;
-            afrag[mt][2 * c][2] = lo.y; afrag[mt][2 * c][3] = hi.y;
-            afrag[mt][2 * c + 1][0] = lo.z; afrag[mt][2 * c + 1][1] = hi.z;
-            afrag[mt][2 * c + 1][2] = lo.w; afrag[mt][2 * c + 1][3] = hi.w;
-          }
-        }
-      }
-      if (m.q0 == 0) score_acc = 0.0f;
-#pragma unroll
-      for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) { run[mt][h] = neg_inf(); idx[mt][h] = 0; }
-    }
-
-    if (!mbar_wait(bars_u32 + 8 * s, parity)) break;
-
-    float acc[2][2][4];
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) acc[mt][nt][r] = 0.0f;
-
-    const uint32_t stage = ring_u32 + s * kStageBytes + tq * 16;
-#pragma unroll
-    for (int nt = 0; nt < 2; ++nt) {
-      const uint32_t rowaddr = stage + (nt * 8 + g) * kRowBytes;
-#pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        const uint4 b = lds_v4(rowaddr + c * 64);
-        mma16816<T>(acc[0][nt], afrag[0][2 * c][0], afrag[0][2 * c][1], afrag[0][2 * c][2],
-                    afrag[0][2 * c][3], b.x, b.y);
-        mma16816<T>(acc[0][nt], afrag[0][2 * c + 1][0], afrag[0][2 * c + 1][1],
-                    afrag[0][2 * c + 1][2], afrag[0][2 * c + 1][3], b.z, b.w);
-        if (rows > 16) {
-          mma16816<T>(acc[1][nt], afrag[1][2 * c][0], afrag[1][2 * c][1], afrag[1][2 * c][2],
-                      afrag[1][2 * c][3], b.x, b.y);
-          mma16816<T>(acc[1][nt], afrag[1][2 * c + 1][0], afrag[1][2 * c + 1][1],
-                      afrag[1][2 * c + 1][2], afrag[1][2 * c + 1][3], b.z, b.w);
-        }
-      }
-    }
-
-    // running max / first argmax; columns visited in ascending order per row
-    const bool full = (m.j0 + kTileTokens <= m.Ld);
-#pragma unroll
-    for (int mt = 0; mt < 2; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < 2; ++nt)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const int col = m.j0 + nt * 8 + tq * 2 + (r & 1);
-          const int h = r >> 1;
-          const float v = acc[mt][nt][r];
-          if (full || col < m.Ld) {
-            if (ARGMAX) {
-              if (v > run[mt][h]) { run[mt][h] = v; idx[mt][h] = col; }
-            } else {
-              run[mt][h] = fmaxf(run[mt][h], v);  // returns the non-NaN operand
+            for (int c = 0; c < kChunks; ++c) {
+              uint4 lo = make_uint4(0, 0, 0, 0), hi = make_uint4(0, 0, 0, 0);
+              if (r_lo < rows) lo = ldg_nc_v4(qp + r_lo * kRowBytes + c * 64);
+              if (r_hi < rows) hi = ldg_nc_v4(qp + r_hi * kRowBytes + c * 64);
+              afrag[mt][2 * c][0] = lo.x; afrag[mt][2 * c][1] = hi.x;
+              afrag[mt][2 * c][2] = lo.y; afrag[mt][2 * c][3] = hi.y;
+              afrag[mt][2 * c + 1][0] = lo.z; afrag[mt][2 * c + 1][1] = hi.z;
+              afrag[mt][2 * c + 1][2] = lo.w; afrag[mt][2 * c + 1][3] = hi.w;
             }
           }
         }
+        if (q0 == 0) score_acc = 0.0f;
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) { run[mt][h] = neg_inf(); idx[mt][h] = 0; }
+      }
+      const int rows = a_rows;
 
-    if (m.j0 + kTileTokens >= m.Ld) {
-      // document finished for this query pass: fold the quad, sum the rows
-      float contrib = 0.0f;
-      int my_ix = 0;
+      if (!mbar_wait(bars_u32 + 8 * s, parity)) break;
+
+      float acc[2][2][4];
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          float v = run[mt][h];
-          int ix = idx[mt][h];
+        for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-          for (int off = 1; off <= 2; off <<= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, v, off);
-            const int oi = __shfl_xor_sync(0xffffffffu, ix, off);
-            if (ARGMAX) merge_best(v, ix, ov, oi);
-            else v = fmaxf(v, ov);
-          }
-          const int row = mt * 16 + h * 8 + g;
-          if (tq == 0 && row < rows) contrib += v;
-          if (tq == mt * 2 + h) my_ix = ix;
-        }
-#pragma unroll
-      for (int off = 16; off > 0; off >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, off);
-      score_acc += contrib;
-      if (ARGMAX) {
-        const int row = (tq >> 1) * 16 + (tq & 1) * 8 + g;
-        if (row < rows) argmax[(int64_t)m.pair * t.q_slots + m.q0 + row] = my_ix;
-      }
-      if (m.q0 + 32 >= m.Lq) {
-        if (lane == 0) scores[m.pair] = score_acc;
-        if (ARGMAX) {
-          for (int sl = m.Lq + lane; sl < t.q_slots; sl += 32)
-            argmax[(int64_t)m.pair * t.q_slots + sl] = 0;
-        }
-      }
-    }
+          for (int r = 0; r < 4; ++r) acc[mt][nt][r] = 0.0f;
 
-    __syncwarp();
+      const uint32_t stage = ring_u32 + s * kStageBytes + tq * 16;
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        const uint4 b0 = lds_v4(stage + g * kRowBytes + c * 64);
+        const uint4 b1 = lds_v4(stage + (8 + g) * kRowBytes + c * 64);
+        mma16816<T>(acc[0][0], afrag[0][2 * c][0], afrag[0][2 * c][1], afrag[0][2 * c][2],
+                    afrag[0][2 * c][3], b0.x, b0.y);
+        mma16816<T>(acc[0][1], afrag[0][2 * c][0], afrag[0][2 * c][1], afrag[0][2 * c][2],
+                    afrag[0][2 * c][3], b1.x, b1.y);
+        if (rows > 16) {
+          mma16816<T>(acc[1][0], afrag[1][2 * c][0], afrag[1][2 * c][1], afrag[1][2 * c][2],
+                      afrag[1][2 * c][3], b0.x, b0.y);
+          mma16816<T>(acc[1][1], afrag[1][2 * c][0], afrag[1][2 * c][1], afrag[1][2 * c][2],
+                      afrag[1][2 * c][3], b1.x, b1.y);
+        }
+        mma16816<T>(acc[0][0], afrag[0][2 * c + 1][0], afrag[0][2 * c + 1][1],
+                    afrag[0][2 * c + 1][2], afrag[0][2 * c + 1][3], b0.z, b0.w);
+        mma16816<T>(acc[0][1], afrag[0][2 * c + 1][0], afrag[0][2 * c + 1][1],
+                    afrag[0][2 * c + 1][2], afrag[0][2 * c + 1][3], b1.z, b1.w);
+        if (rows > 16) {
+          mma16816<T>(acc[1][0], afrag[1][2 * c + 1][0], afrag[1][2 * c + 1][1],
+                      afrag[1][2 * c + 1][2], afrag[1][2 * c + 1][3], b0.z, b0.w);
+          mma16816<T>(acc[1][1], afrag[1][2 * c + 1][0], afrag[1][2 * c + 1][1],
+                      afrag[1][2 * c + 1][2], afrag[1][2 * c + 1][3], b1.z, b1.w);
+        }
+      }
+
+      // running max / first argmax; a thread meets its columns in ascending order
+      if (j0 + kTileTokens <= Ld) {
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              const int h = r >> 1;
+              const float v = acc[mt][nt][r];
+              if (ARGMAX) {
+                if (v > run[mt][h]) { run[mt][h] = v; idx[mt][h] = j0 + nt * 8 + tq * 2 + (r & 1); }
+              } else {
+                run[mt][h] = fmaxf(run[mt][h], v);  // returns the non-NaN operand
+              }
+            }
+      } else {
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+              const int col = j0 + nt * 8 + tq * 2 + (r & 1);
+              const int h = r >> 1;
+              const float v = acc[mt][nt][r];
+              if (col < Ld) {
+                if (ARGMAX) {
+                  if (v > run[mt][h]) { run[mt][h] = v; idx[mt][h] = col; }
+                } else {
+                  run[mt][h] = fmaxf(run[mt][h], v);
+                }
+              }
+            }
+      }
+
+      if (j0 + kTileTokens >= Ld) {
+        // document finished for this query pass: fold the quad, sum the rows
+        float contrib = 0.0f;
+        int my_ix = 0;
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            float v = run[mt][h];
+            int ix = idx[mt][h];
+#pragma unroll
+            for (int off = 1; off <= 2; off <<= 1) {
+              const float ov = __shfl_xor_sync(0xffffffffu, v, off);
+              if (ARGMAX) {
+                const int oi = __shfl_xor_sync(0xffffffffu, ix, off);
+                merge_best(v, ix, ov, oi);
+              } else {
+                v = fmaxf(v, ov);
+              }
+            }
+            const int row = mt * 16 + h * 8 + g;
+            if (tq == 0 && row < rows) contrib += v;
+            if (tq == mt * 2 + h) my_ix = ix;
+          }
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) contrib += __shfl_xor_sync(0xffffffffu, contrib, off);
+        score_acc += contrib;
+        if (ARGMAX) {
+          const int row = (tq >> 1) * 16 + (tq & 1) * 8 + g;
+          if (row < rows) argmax[(int64_t)m.pair * t.q_slots + q0 + row] = my_ix;
+        }
+        if (q0 + 32 >= Lq) {
+          if (lane == 0) scores[m.pair] = score_acc;
+          if (ARGMAX) {
+            for (int sl = Lq + lane; sl < t.q_slots; sl += 32)
+              argmax[(int64_t)m.pair * t.q_slots + sl] = 0;
+          }
+        }
+      }
+      __syncwarp();  // every lane is done with slot s before lane 0 refills it
+    }
     feed(s);
-    __syncwarp();
+    if (it < kStages) __syncwarp();
   }
 }
 
