@@ -139,7 +139,10 @@ int run_forward(const PairTable& t, float* scores, int32_t* argmax, int dtype, v
   const int path = g_forward_path.load(std::memory_order_relaxed);
 
   if (LAYOUT == kContrastive && path != 1 && path != 2 && tc05_eligible(t, dtype)) {
-    return launch_tc05<ARGMAX>(t, scores, argmax, dtype, st);
+    const int rc = launch_tc05<ARGMAX>(t, scores, argmax, dtype, sm_count(), st);
+    if (rc == 0) return launch_check("fwd_tc05_kernel");
+    if (rc < 0) return fail(MAXSIM_ECUDA, "could not configure the tcgen05 kernel");
+    // rc == 1: tensor maps could not be encoded; use the streaming kernel
   }
   if (path == 3 && LAYOUT == kContrastive)
     return fail(MAXSIM_EUNSUPPORTED, "tcgen05 kernel forced but shape not eligible");
@@ -240,11 +243,12 @@ int run_backward(const PairTable& t, const float* dscore, const int32_t* argmax,
 
 PairTable packed_table(const void* q, const int32_t* qoff, const void* d, const int32_t* doff,
                        const int32_t* pq, const int32_t* pd, int64_t n_pairs, int64_t dim,
-                       int64_t max_q_len) {
+                       int64_t max_q_len, int64_t q_rows, int64_t d_rows) {
   PairTable t{};
   t.queries = q; t.documents = d;
   t.ia = qoff; t.ib = doff; t.ic = pq; t.id = pd;
   t.n_pairs = n_pairs; t.dim = (int32_t)dim; t.q_slots = (int32_t)max_q_len;
+  t.q_rows = q_rows; t.d_rows = d_rows;
   t.Ld_max = 0; t.C = 1;
   return t;
 }
@@ -255,16 +259,18 @@ PairTable padded_table(const void* q, const int32_t* qlen, const void* d, const 
   t.queries = q; t.documents = d;
   t.ia = qlen; t.ib = dlen; t.ic = nullptr; t.id = nullptr;
   t.n_pairs = B * C; t.dim = (int32_t)dim; t.q_slots = (int32_t)Lq_max;
+  t.q_rows = B * Lq_max; t.d_rows = B * C * Ld_max;
   t.Ld_max = (int32_t)Ld_max; t.C = (int32_t)(C > 0 ? C : 1);
   return t;
 }
 
 PairTable contrastive_table(const void* q, const void* d, const int32_t* doff, int64_t Nq,
-                            int64_t Lq, int64_t Nb, int64_t dim) {
+                            int64_t Lq, int64_t Nb, int64_t dim, int64_t d_rows) {
   PairTable t{};
   t.queries = q; t.documents = d;
   t.ia = nullptr; t.ib = doff; t.ic = nullptr; t.id = nullptr;
   t.n_pairs = Nq * Nb; t.dim = (int32_t)dim; t.q_slots = (int32_t)Lq;
+  t.q_rows = Nq * Lq; t.d_rows = d_rows;
   t.Ld_max = 0; t.C = (int32_t)(Nb > 0 ? Nb : 1);
   return t;
 }
@@ -302,7 +308,8 @@ int maxsim_forward(const void* queries, const int32_t* query_offsets, const void
     return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
   if (max_q_len <= 0) return fail(MAXSIM_EINVAL, "max_q_len must be > 0; got %lld", (long long)max_q_len);
   PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
-                             pair_document_ids, n_pairs, dim, max_q_len);
+                             pair_document_ids, n_pairs, dim, max_q_len, total_q_tokens,
+                             total_d_tokens);
   return run_forward<kPacked, false>(t, scores, nullptr, dtype, stream);
 }
 
@@ -319,7 +326,8 @@ int maxsim_packed_forward_with_argmax(const void* queries, const int32_t* query_
     return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
   if (max_q_len <= 0) return fail(MAXSIM_EINVAL, "max_q_len must be > 0; got %lld", (long long)max_q_len);
   PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
-                             pair_document_ids, n_pairs, dim, max_q_len);
+                             pair_document_ids, n_pairs, dim, max_q_len, total_q_tokens,
+                             total_d_tokens);
   return run_forward<kPacked, true>(t, scores, argmax, dtype, stream);
 }
 
@@ -334,7 +342,8 @@ int maxsim_packed_backward(const float* dscore, const void* queries, const int32
   if (!fits_i32(dim) || !fits_i32(max_q_len) || !fits_i32(total_q_tokens) || !fits_i32(total_d_tokens))
     return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
   PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
-                             pair_document_ids, n_pairs, dim, max_q_len);
+                             pair_document_ids, n_pairs, dim, max_q_len, total_q_tokens,
+                             total_d_tokens);
   return run_backward<kPacked>(t, dscore, argmax, grad_queries, grad_documents, total_q_tokens,
                                total_d_tokens, 0, dtype, stream);
 }
@@ -381,7 +390,8 @@ int maxsim_contrastive_forward(const void* queries, const void* documents,
   if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
       !fits_i32(total_d_tokens))
     return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
-  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim);
+  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim,
+                                  total_d_tokens);
   return run_forward<kContrastive, false>(t, scores, nullptr, dtype, stream);
 }
 
@@ -393,7 +403,8 @@ int maxsim_contrastive_forward_with_argmax(const void* queries, const void* docu
   if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
       !fits_i32(total_d_tokens))
     return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
-  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim);
+  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim,
+                                  total_d_tokens);
   return run_forward<kContrastive, true>(t, scores, argmax, dtype, stream);
 }
 
@@ -405,7 +416,8 @@ int maxsim_contrastive_backward(const float* dscore, const void* queries, const 
   if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
       !fits_i32(total_d_tokens))
     return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
-  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim);
+  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim,
+                                  total_d_tokens);
   return run_backward<kContrastive>(t, dscore, argmax, grad_queries, grad_documents, Nq * Lq,
                                     total_d_tokens, Nq, dtype, stream);
 }

@@ -29,6 +29,8 @@ struct PairTable {
   const int32_t* ic;
   const int32_t* id;
   int64_t n_pairs;
+  int64_t q_rows;    // total query token rows
+  int64_t d_rows;    // total document token rows
   int32_t dim;
   int32_t q_slots;   // argmax slots per pair: Lq_max / max_q_len / Lq
   int32_t Ld_max;    // padded only

@@ -1,13 +1,437 @@
-// tcgen05 / TMEM contrastive forward.
+// Contrastive forward on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// All-pairs scoring of rectangular queries [Nq, 32, 128] against packed
+// documents [T_d, 128] is a dense contraction with only 256 flop per
+// similarity value, so the kernel is organised around keeping the tensor pipe
+// fed and consuming its output at the rate it is produced:
+//
+//   * one CTA per SM, M = 256: two accumulators of 128 TMEM lanes, each lane a
+//     (query, query-token) row -- 4 queries x 32 tokens per accumulator;
+//   * the packed document stream is cut into tiles of 128 tokens that ignore
+//     document boundaries, so no MMA column is spent on padding;
+//   * warp 0 stages tiles with TMA (cp.async.bulk.tensor, 128-byte swizzle)
+//     into a 4-deep shared-memory ring; warp 1 issues tcgen05.mma (K = 128 as
+//     8 steps of 16) for both accumulators against each staged tile and
+//     commits to mbarriers; accumulators are double-buffered in TMEM (512
+//     columns) so the tensor pipe runs ahead of the epilogue;
+//   * eight epilogue warps read their row's 128 similarities per tile with
+//     tcgen05.ld and fold them into a running maximum and first-index argmax
+//     held in registers, cutting at document boundaries; when a document ends
+//     the 32 row maxima of a query are summed with a warp shuffle tree.
+//     No similarity value is ever written to shared or global memory.
+//
+// Every wait is bounded; a wait that runs out records a status bit and the
+// CTA drains to the common exit, where TMEM is released.
 #pragma once
 
+#include <cuda.h>
+
 #include "common.cuh"
+#include "fwd_mma.cuh"
 
 namespace maxsim {
+namespace tc05 {
 
-inline bool tc05_eligible(const PairTable&, int) { return false; }
+constexpr int kBM = 128;   // rows per accumulator
+constexpr int kMSub = 2;   // accumulators per CTA
+constexpr int kLq = 32;
+constexpr int kQPerSub = kBM / kLq;          // 4 queries per accumulator
+constexpr int kQPerCta = kQPerSub * kMSub;   // 8
+constexpr int kBN = 128;   // document tokens per tile
+constexpr int kDim = 128;
+constexpr int kBStages = 4;
+constexpr int kAccStages = 2;
+constexpr int kEpiWarps = 4 * kMSub;
+constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kTmemCols = kMSub * kBN * kAccStages;  // 512
+constexpr int kHalfBytes = kBM * 128;                // one 128-row x 64-element box: 16 KB
+constexpr int kTileBytes = 2 * kHalfBytes;           // 32 KB
+constexpr uint32_t kWaitLimit = 1u << 22;
+
+constexpr size_t kSmemA = (size_t)kMSub * kTileBytes;
+constexpr size_t kSmemB = (size_t)kBStages * kTileBytes;
+constexpr size_t kSmemBytes = kSmemA + kSmemB + 1024 /*alignment slack*/ + 256 /*barriers*/;
+
+__device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kWaitLimit; ++it) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  atomicOr(&g_device_status, 2);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows of
+// 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address
+  d |= (uint64_t)1 << 16;                        // leading-dim offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride between 8-row groups
+  d |= (uint64_t)1 << 46;                        // descriptor version
+  d |= (uint64_t)2 << 61;                        // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct Params {
+  const int32_t* doc_offsets;
+  float* scores;
+  int32_t* argmax;
+  int32_t Nq, Nb;
+  int32_t n_qgroups;      // ceil(Nq / 8)
+  int32_t docs_per_item;
+  int32_t n_items;
+  uint32_t idesc;
+};
 
 template <bool ARGMAX>
-int launch_tc05(const PairTable&, float*, int32_t*, int, cudaStream_t) { return -2; }
+__global__ void __launch_bounds__(kThreads, 1)
+fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_d,
+                const Params P) {
+  extern __shared__ unsigned char tc05_smem_raw[];
+  const uint32_t raw = smem_u32(tc05_smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  const uint32_t smA = base;
+  const uint32_t smB = base + (uint32_t)kSmemA;
+  const uint32_t bars = smB + (uint32_t)kSmemB;
+  // barrier slots (8 bytes each)
+  const uint32_t b_full = bars;                        // [kBStages]
+  const uint32_t b_empty = bars + 8 * kBStages;        // [kBStages]
+  const uint32_t a_full = bars + 16 * kBStages;
+  const uint32_t a_empty = a_full + 8;
+  const uint32_t t_full = a_empty + 8;                 // [kAccStages]
+  const uint32_t t_empty = t_full + 8 * kAccStages;    // [kAccStages]
+  const uint32_t tmem_slot = t_empty + 8 * kAccStages; // 4 bytes
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kBStages; ++i) { mbar_init(b_full + 8 * i, 1); mbar_init(b_empty + 8 * i, 1); }
+    mbar_init(a_full, 1);
+    mbar_init(a_empty, 1);
+    for (int i = 0; i < kAccStages; ++i) {
+      mbar_init(t_full + 8 * i, 1);
+      mbar_init(t_empty + 8 * i, kEpiWarps);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(tmem_slot), "r"((uint32_t)kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  uint32_t tmem_base;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
+
+  const int32_t* __restrict__ doff = P.doc_offsets;
+
+  if (warp == 0) {
+    // ===================== TMA producer ====================================
+    if (lane == 0) {
+      uint32_t bs = 0, bph = 0, iter = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < P.n_items; item += gridDim.x, ++iter) {
+        const int dc = item / P.n_qgroups, qg = item - dc * P.n_qgroups;
+        const int d_lo = dc * P.docs_per_item, d_hi = min(P.Nb, d_lo + P.docs_per_item);
+        const int s0 = __ldg(doff + d_lo), s1 = __ldg(doff + d_hi);
+        const int ntiles = (s1 - s0 + kBN - 1) / kBN;
+        if (!wait_bounded(a_empty, (iter & 1u) ^ 1u)) { ok = false; break; }
+        mbar_expect_tx(a_full, (uint32_t)kSmemA);
+#pragma unroll
+        for (int sub = 0; sub < kMSub; ++sub)
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+            tma_load_2d(smA + sub * kTileBytes + h * kHalfBytes, &tm_q, h * 64,
+                        (qg * kMSub + sub) * kBM, a_full);
+        for (int tile = 0; tile < ntiles; ++tile) {
+          if (!wait_bounded(b_empty + 8 * bs, bph ^ 1u)) { ok = false; break; }
+          mbar_expect_tx(b_full + 8 * bs, (uint32_t)kTileBytes);
+#pragma unroll
+          for (int h = 0; h < 2; ++h)
+            tma_load_2d(smB + bs * kTileBytes + h * kHalfBytes, &tm_d, h * 64, s0 + tile * kBN,
+                        b_full + 8 * bs);
+          if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ===================== MMA issuer ======================================
+    if (lane == 0) {
+      uint32_t bs = 0, bph = 0, acc = 0, aph = 0, iter = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; ok && item < P.n_items; item += gridDim.x, ++iter) {
+        const int dc = item / P.n_qgroups;
+        const int d_lo = dc * P.docs_per_item, d_hi = min(P.Nb, d_lo + P.docs_per_item);
+        const int s0 = __ldg(doff + d_lo), s1 = __ldg(doff + d_hi);
+        const int ntiles = (s1 - s0 + kBN - 1) / kBN;
+        if (!wait_bounded(a_full, iter & 1u)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int tile = 0; tile < ntiles; ++tile) {
+          if (!wait_bounded(t_empty + 8 * acc, aph ^ 1u)) { ok = false; break; }
+          if (!wait_bounded(b_full + 8 * bs, bph)) { ok = false; break; }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+          for (int sub = 0; sub < kMSub; ++sub) {
+            const uint32_t d_tmem = tmem_base + acc * (kMSub * kBN) + sub * kBN;
+#pragma unroll
+            for (int k = 0; k < kDim / 16; ++k) {
+              const uint32_t koff = (k >> 2) * kHalfBytes + (k & 3) * 32;
+              const uint64_t ad = umma_desc(smA + sub * kTileBytes + koff);
+              const uint64_t bd = umma_desc(smB + bs * kTileBytes + koff);
+              umma_f16(d_tmem, ad, bd, P.idesc, k > 0 ? 1u : 0u);
+            }
+          }
+          umma_commit(b_empty + 8 * bs);  // slot reusable once these MMAs retire
+          umma_commit(t_full + 8 * acc);  // accumulators ready for the epilogue
+          if (++bs == kBStages) { bs = 0; bph ^= 1u; }
+          if (++acc == kAccStages) { acc = 0; aph ^= 1u; }
+        }
+        umma_commit(a_empty);  // query block reusable once this item's MMAs retire
+      }
+    }
+  } else {
+    // ===================== epilogue ========================================
+    const int ew = warp - 2;
+    const int sub = ew >> 2;
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    uint32_t acc = 0, aph = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; ok && item < P.n_items; item += gridDim.x) {
+      const int dc = item / P.n_qgroups, qg = item - dc * P.n_qgroups;
+      const int d_lo = dc * P.docs_per_item, d_hi = min(P.Nb, d_lo + P.docs_per_item);
+      const int s0 = __ldg(doff + d_lo), s1 = __ldg(doff + d_hi);
+      const int ntiles = (s1 - s0 + kBN - 1) / kBN;
+      const int q = (qg * kMSub + sub) * kQPerSub + quad;  // this warp's query
+      const bool q_ok = q < P.Nq;
+
+      int d = d_lo;
+      int dstart = s0;
+      int dend = __ldg(doff + d_lo + 1);
+      float run = neg_inf();
+      int idx = 0;
+
+      for (int tile = 0; tile < ntiles; ++tile) {
+        if (!wait_bounded(t_full + 8 * acc, aph)) { ok = false; break; }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t taddr0 =
+            tmem_base + ((uint32_t)(quad * 32) << 16) + acc * (kMSub * kBN) + sub * kBN;
+#pragma unroll 1
+        for (int c4 = 0; c4 < kBN / 32; ++c4) {
+          const int tok0 = s0 + tile * kBN + c4 * 32;
+          if (tok0 >= s1 || d >= d_hi) break;  // uniform: nothing left in this item
+          float v[32];
+          tmem_ld32(taddr0 + c4 * 32, v);
+          int col = 0;
+          while (col < 32 && d < d_hi) {
+            const int seg_end = min(32, dend - tok0);
+            const int base_ix = tok0 - dstart;
+            if (col == 0 && seg_end == 32) {
+              float m = v[0];
+#pragma unroll
+              for (int j = 1; j < 32; ++j) m = fmaxf(m, v[j]);
+              if (ARGMAX) {
+                if (m > run) {
+                  run = m;
+                  int first = 31;
+#pragma unroll
+                  for (int j = 30; j >= 0; --j) first = (v[j] == m) ? j : first;
+                  idx = base_ix + first;
+                }
+              } else {
+                run = fmaxf(run, m);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (j >= col && j < seg_end) {
+                  if (ARGMAX) {
+                    if (v[j] > run) { run = v[j]; idx = base_ix + j; }
+                  } else {
+                    run = fmaxf(run, v[j]);
+                  }
+                }
+              }
+            }
+            col = max(col, seg_end);
+            if (tok0 + col >= dend) {
+              // document d complete for this warp's query
+              float sum = run;
+#pragma unroll
+              for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+              if (q_ok) {
+                const int64_t pair = (int64_t)q * P.Nb + d;
+                if (ARGMAX) P.argmax[pair * kLq + lane] = idx;
+                if (lane == 0) P.scores[pair] = sum;
+              }
+              run = neg_inf();
+              idx = 0;
+              ++d;
+              dstart = dend;
+              if (d < d_hi) dend = __ldg(doff + d + 1);
+            }
+          }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(t_empty + 8 * acc);
+        if (++acc == kAccStages) { acc = 0; aph ^= 1u; }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem_base), "r"((uint32_t)kTmemCols)
+                 : "memory");
+  }
+}
+
+}  // namespace tc05
+
+// ---------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------
+typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                      const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                      const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline TensorMapEncodeFn tensor_map_encoder() {
+  static TensorMapEncodeFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<TensorMapEncodeFn>(p);
+  }
+  return fn;
+}
+
+// rows x 128 row-major matrix of 16-bit elements, boxes of 128 rows x 64 elements
+inline bool encode_rows128(CUtensorMap* map, const void* base, int64_t rows, bool bf16) {
+  TensorMapEncodeFn enc = tensor_map_encoder();
+  if (!enc || rows <= 0) return false;
+  cuuint64_t gdim[2] = {(cuuint64_t)tc05::kDim, (cuuint64_t)rows};
+  cuuint64_t gstride[1] = {(cuuint64_t)tc05::kDim * 2};
+  cuuint32_t box[2] = {64, (cuuint32_t)tc05::kBM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                   const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+inline bool tc05_eligible(const PairTable& t, int dtype) {
+  if (dtype != 1 && dtype != 2) return false;  // fp16 / bf16
+  if (t.dim != tc05::kDim || t.q_slots != tc05::kLq) return false;
+  if ((reinterpret_cast<uintptr_t>(t.queries) & 15u) || (reinterpret_cast<uintptr_t>(t.documents) & 15u))
+    return false;
+  const int64_t Nb = t.C, Nq = t.n_pairs / (Nb > 0 ? Nb : 1);
+  if (Nq < tc05::kQPerCta || Nb < 1) return false;
+  if (t.d_rows <= 0 || t.d_rows >= (1ll << 31) || Nq * tc05::kLq >= (1ll << 31)) return false;
+  return tensor_map_encoder() != nullptr;
+}
+
+// Returns 0 on success, 1 if the launch could not be prepared (caller falls
+// back to another kernel), or a CUDA error code < 0.
+template <bool ARGMAX>
+int launch_tc05(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
+                cudaStream_t st) {
+  const int64_t Nb = t.C, Nq = t.n_pairs / Nb;
+  CUtensorMap tm_q, tm_d;
+  const bool bf16 = dtype == 2;
+  if (!encode_rows128(&tm_q, t.queries, Nq * tc05::kLq, bf16)) return 1;
+  if (!encode_rows128(&tm_d, t.documents, t.d_rows, bf16)) return 1;
+
+  tc05::Params P;
+  P.doc_offsets = t.ib;
+  P.scores = scores;
+  P.argmax = argmax;
+  P.Nq = (int32_t)Nq;
+  P.Nb = (int32_t)Nb;
+  P.n_qgroups = (int32_t)((Nq + tc05::kQPerCta - 1) / tc05::kQPerCta);
+  int64_t dpi = (Nb * (int64_t)P.n_qgroups) / (16ll * sms);
+  if (dpi < 1) dpi = 1;
+  if (dpi > Nb) dpi = Nb;
+  P.docs_per_item = (int32_t)dpi;
+  const int64_t n_dc = (Nb + dpi - 1) / dpi;
+  const int64_t n_items = n_dc * P.n_qgroups;
+  if (n_items >= (1ll << 31)) return 1;
+  P.n_items = (int32_t)n_items;
+  const uint32_t fmt = bf16 ? 1u : 0u;
+  P.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(tc05::kBN >> 3) << 17) |
+            ((uint32_t)(tc05::kBM >> 4) << 24);
+
+  auto kern = tc05::fwd_tc05_kernel<ARGMAX>;
+  static bool configured[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -3;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)tc05::kSmemBytes) != cudaSuccess)
+      return -3;
+    if (dev >= 0 && dev < 64) configured[dev] = true;
+  }
+  const int grid = (int)(n_items < sms ? n_items : sms);
+  kern<<<grid, tc05::kThreads, tc05::kSmemBytes, st>>>(tm_q, tm_d, P);
+  return 0;
+}
 
 }  // namespace maxsim
