@@ -278,6 +278,27 @@ def bench_train_steps(dev, peaks, full: bool):
     return out
 
 
+def run_contrastive_profile(args):
+    """A few train steps of the contrastive-with-ties configuration, nothing
+    else: the command a profiler wraps."""
+    import maxsim_b200 as maxsim
+    from maxsim_b200 import workloads as W
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    n = 512 if args.small else 1024
+    data = W.c5_device(dev, Nq=n, Nb=n)
+    q = data["queries"].requires_grad_(True)
+    d = data["documents"].requires_grad_(True)
+    off = data["document_offsets"]
+    target = torch.arange(n, device=dev)
+    for _ in range(max(1, args.warmup)):
+        contrastive_train_step(maxsim, q, d, off, target)
+    ms = _event_ms(lambda: contrastive_train_step(maxsim, q, d, off, target), max(1, args.steps))
+    print(json.dumps({"profile_run": True, "workload": "c5_contrastive_ties_bf16", "Nq": n, "Nb": n,
+                      "doc_tokens": int(d.shape[0]), "ms_per_step": statistics.median(ms)}), flush=True)
+
+
 def run_gpu_arm(args):
     import maxsim_b200 as maxsim
     from maxsim_b200 import _ops
@@ -450,9 +471,14 @@ def main():
                     help="16 queries per GPU instead of 256 (for profiler captures; not a bench value)")
     ap.add_argument("--kernel-only", action="store_true",
                     help="run only the device-resident loop (for profiler captures)")
+    ap.add_argument("--profile-contrastive", action="store_true",
+                    help="run only contrastive forward+backward steps of the ties configuration "
+                         "(Nq=Nb=1024, or 512 with --small); for profiler captures")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.profile_contrastive:
+        run_contrastive_profile(args)
     else:
         run_gpu_arm(args)
 

@@ -184,8 +184,16 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
     }
     {
       const int64_t grid = (q_rows + kBwdWarps - 1) / kBwdWarps;
-      bwd_dq_gather_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq,
-                                                                           q_rows, vec_ok);
+      bool fast = false;
+      if constexpr (sizeof(T) == 2) {
+        fast = vec_ok && dim <= 128 && dim % 8 == 0 && d_rows < (1ll << 31);
+        if (fast)
+          bwd_dq_gather16_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq,
+                                                                                 q_rows);
+      }
+      if (!fast)
+        bwd_dq_gather_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq,
+                                                                             q_rows, vec_ok);
       int rc = launch_check("bwd_dq_gather_kernel");
       if (rc) return rc;
     }
@@ -194,26 +202,25 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
       bwd_dd_padded_kernel<T><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dd, vec_ok);
       return launch_check("bwd_dd_padded_kernel");
     } else {
-      const size_t smem = (size_t)kSegTokens * dim * sizeof(float);
-      if (smem <= 200 * 1024) {
-        // longest document decides how many token chunks each document gets
-        // (documents shorter than that exit early).  The host does not know
-        // the lengths, so size by the worst case total_d_tokens bound.
-        auto kern = bwd_dd_contrastive_kernel<T>;
-        if (smem > 48 * 1024)
+      const int64_t Nb = t.C;
+      if (vec_ok && dim % 8 == 0 && t.q_slots <= kInvEntries && Nq < (1ll << 31) &&
+          Nb < (1ll << 31) && Nq * (int64_t)t.q_slots < (1ll << 31)) {
+        auto kern = bwd_dd_invert_kernel<T>;
+        constexpr size_t smem = inv_smem_bytes();
+        static bool configured[64] = {false};
+        int dev = 0;
+        MAXSIM_CUDA(cudaGetDevice(&dev));
+        if (dev < 0 || dev >= 64 || !configured[dev]) {
           MAXSIM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        // d_rows tokens over Nb documents, each >= 1 token: no document is
-        // longer than d_rows - (Nb - 1).
-        const int64_t Nb = t.C;
-        int64_t longest = d_rows - (Nb - 1);
-        if (longest < 1) longest = 1;
-        int64_t max_chunks = (longest + kSegTokens - 1) / kSegTokens;
-        // Launch-size guard: very skewed batches fall back to atomics.
-        if (max_chunks * Nb <= (1ll << 24) && max_chunks <= 64) {
-          kern<<<(unsigned)(max_chunks * Nb), kSegWarps * 32, smem, st>>>(t, dscore, argmax, dd, Nq,
-                                                                          (int)max_chunks, vec_ok);
-          return launch_check("bwd_dd_contrastive_kernel");
+          if (dev >= 0 && dev < 64) configured[dev] = true;
         }
+        // One CTA per document.  Documents longer than kInvBins tokens are
+        // covered by the kernel's stride over token chunks; a second CTA row
+        // helps only when the mean document is that long.
+        const int gy = (d_rows / Nb > kInvBins) ? 2 : 1;
+        dim3 grid((unsigned)Nb, (unsigned)gy);
+        kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq);
+        return launch_check("bwd_dd_invert_kernel");
       }
       MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
       const int64_t grid = (t.n_pairs + kBwdWarps - 1) / kBwdWarps;

@@ -49,6 +49,38 @@ __device__ __forceinline__ void store4(float* __restrict__ p, bool vec, int k, i
   }
 }
 
+// Eight consecutive elements of a token row, kept packed in registers until
+// they are used (a 16-bit row costs 4 registers, so eight rows can be in flight
+// per lane).
+template <typename T>
+struct Row8 {
+  uint4 a;
+  __device__ __forceinline__ void load(const T* __restrict__ p) {
+    a = __ldg(reinterpret_cast<const uint4*>(p));
+  }
+  __device__ __forceinline__ void zero() { a = make_uint4(0, 0, 0, 0); }
+  __device__ __forceinline__ void fma_into(float g, float (&acc)[8]) const {
+    const T* e = reinterpret_cast<const T*>(&a);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = fmaf(g, to_f32(e[i]), acc[i]);
+  }
+};
+template <>
+struct Row8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* __restrict__ p) {
+    a = __ldg(reinterpret_cast<const float4*>(p));
+    b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  }
+  __device__ __forceinline__ void zero() { a = make_float4(0, 0, 0, 0); b = a; }
+  __device__ __forceinline__ void fma_into(float g, float (&acc)[8]) const {
+    acc[0] = fmaf(g, a.x, acc[0]); acc[1] = fmaf(g, a.y, acc[1]);
+    acc[2] = fmaf(g, a.z, acc[2]); acc[3] = fmaf(g, a.w, acc[3]);
+    acc[4] = fmaf(g, b.x, acc[4]); acc[5] = fmaf(g, b.y, acc[5]);
+    acc[6] = fmaf(g, b.z, acc[6]); acc[7] = fmaf(g, b.w, acc[7]);
+  }
+};
+
 // ---------------------------------------------------------------------------
 // grad_q by gather (padded: over the C candidates of query b; contrastive:
 // over the Nb documents).  One warp per query row; lanes own 4 consecutive
@@ -98,19 +130,107 @@ bwd_dq_gather_kernel(PairTable t, const float* __restrict__ dscore,
           }
         }
         const int n = min(32, C - c0);
-        for (int l = 0; l < n; ++l) {
-          const float gv = __shfl_sync(0xffffffffu, gl, l);
-          const int64_t sr = __shfl_sync(0xffffffffu, src, l);
-          if (sr >= 0 && k < dim) {
-            float dv[4];
-            load4<T>(D + sr * dim, vec, k, dim, dv);
+        // eight independent row loads in flight per lane before their FMAs
+        for (int l0 = 0; l0 < n; l0 += 8) {
+          float dv[8][4];
+          float gw[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) acc[e] = fmaf(gv, dv[e], acc[e]);
+          for (int u = 0; u < 8; ++u) {
+            const int l = (l0 + u) & 31;
+            const float gv = __shfl_sync(0xffffffffu, gl, l);
+            const int64_t sr = __shfl_sync(0xffffffffu, src, l);
+            const bool ok = (l0 + u < n) && sr >= 0 && k < dim;
+            gw[u] = ok ? gv : 0.f;
+            if (ok) {
+              load4<T>(D + sr * dim, vec, k, dim, dv[u]);
+            } else {
+              dv[u][0] = dv[u][1] = dv[u][2] = dv[u][3] = 0.f;
+            }
           }
+#pragma unroll
+          for (int u = 0; u < 8; ++u)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(gw[u], dv[u][e], acc[e]);
         }
       }
     }
     if (k < dim) store4(dq + row * dim, vec, k, dim, acc);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// grad_q gather, 16-bit element types with dim <= 128 and dim % 8 == 0.
+// One warp per query row; each half-warp fetches one candidate's winning row
+// with 128-bit loads (16 lanes x 8 elements), so a warp step covers two
+// candidates and four rows are in flight per lane (more in flight costs
+// occupancy and measured slower).
+// ---------------------------------------------------------------------------
+template <typename T, int LAYOUT>
+__global__ void __launch_bounds__(kBwdWarps * 32)
+bwd_dq_gather16_kernel(PairTable t, const float* __restrict__ dscore,
+                       const int32_t* __restrict__ argmax, float* __restrict__ dq,
+                       int64_t n_rows) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  const int lane = threadIdx.x & 31, half = lane >> 4, hl = lane & 15;
+  const int64_t row = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int dim = t.dim, slots = t.q_slots, C = t.C;
+  const int64_t b = row / slots;
+  const int i = (int)(row - b * slots);
+  const int Lq = (LAYOUT == kPadded) ? __ldg(t.ia + b) : slots;
+  const T* D = reinterpret_cast<const T*>(t.documents);
+  const int k = hl * 8;
+  const bool k_ok = k < dim;
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+
+  if (i < Lq) {
+    for (int c0 = 0; c0 < C; c0 += 32) {
+      const int c = c0 + lane;
+      float gl = 0.f;
+      int32_t src = -1;  // winning document row of candidate c0+lane, or -1
+      if (c < C) {
+        const int64_t p = b * C + c;
+        const int j = __ldg(argmax + p * slots + i);
+        int32_t d_row0, Ld;
+        if (LAYOUT == kPadded) {
+          d_row0 = (int32_t)(p * t.Ld_max);
+          Ld = __ldg(t.ib + p);
+        } else {
+          d_row0 = __ldg(t.ib + c);
+          Ld = __ldg(t.ib + c + 1) - d_row0;
+        }
+        if (j >= 0 && j < Ld) {
+          src = d_row0 + j;
+          gl = __ldg(dscore + p);
+        }
+      }
+      const int n = min(32, C - c0);
+      for (int l0 = 0; l0 < n; l0 += 8) {
+        Row8<T> rows[4];
+        float gw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int l = (l0 + 2 * u + half) & 31;
+          const float gv = __shfl_sync(0xffffffffu, gl, l);
+          const int32_t sr = __shfl_sync(0xffffffffu, src, l);
+          const bool ok = (l0 + 2 * u + half < n) && sr >= 0 && k_ok;
+          gw[u] = ok ? gv : 0.f;
+          rows[u].zero();
+          if (ok) rows[u].load(D + (int64_t)sr * dim + k);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) rows[u].fma_into(gw[u], acc);
+      }
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
+  if (half == 0 && k_ok) {
+    float4* out = reinterpret_cast<float4*>(dq + row * dim + k);
+    out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
   }
 }
 
@@ -217,73 +337,168 @@ bwd_route_atomic_kernel(PairTable t, const float* __restrict__ dscore,
 }
 
 // ---------------------------------------------------------------------------
-// grad_d of the contrastive layout by per-document shared-memory accumulation.
-// CTA (d, chunk) owns kSegTokens document tokens of document d; its warps
-// sweep all (query, token) argmax entries of that document, and every entry
-// that lands in the chunk adds g * q_row into a shared fp32 tile with
-// shared-memory reductions.  The tile is stored once, so grad_d needs no zero
-// fill and no global atomics.
+// grad_d of the contrastive layout: invert the argmax in shared memory, then
+// gather.  grad_d[d, j] = sum over the (query, token) entries whose argmax is
+// j of g[q, d] * Q[q, i].  A scatter of that sum would need atomics; instead
+// one CTA per document counting-sorts the document's Nq*Lq argmax entries by
+// winning token inside shared memory (histogram, scan, scatter of entry ids),
+// after which every document token owns a contiguous list of the query rows
+// routed to it.  Warps then take tokens one at a time and sum their lists in
+// registers -- a pure gather (two 128-bit row loads per warp step, eight rows
+// in flight per lane) with exactly one store per gradient row.  No global
+// atomics, no scratch in global memory, no zero-fill pass.
+//
+// Entries are processed in passes of at most kInvEntries (query blocks) and
+// documents longer than kInvBins tokens in token chunks; later passes add to
+// the rows the first pass stored.
 // ---------------------------------------------------------------------------
-constexpr int kSegTokens = 64;
-constexpr int kSegWarps = 8;
+constexpr int kInvThreads = 512;
+constexpr int kInvEntries = 32768;  // entry ids held per pass (128 KB)
+constexpr int kInvBins = 2048;      // document tokens per chunk
+constexpr int kInvMaxQ = 4096;      // queries per pass (g column held in shared memory)
+
+constexpr size_t inv_smem_bytes() {
+  return (size_t)kInvEntries * 4 + (size_t)kInvMaxQ * 4 + (size_t)(2 * kInvBins + 2) * 4 + 16;
+}
 
 template <typename T>
-__global__ void __launch_bounds__(kSegWarps * 32)
-bwd_dd_contrastive_kernel(PairTable t, const float* __restrict__ dscore,
-                          const int32_t* __restrict__ argmax, float* __restrict__ dd,
-                          int64_t Nq, int max_chunks, int vec_ok) {
-  extern __shared__ __align__(16) float seg_smem[];  // [kSegTokens][dim]
+__global__ void __launch_bounds__(kInvThreads, 1)
+bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
+                     const int32_t* __restrict__ argmax, float* __restrict__ dd, int Nq) {
+  extern __shared__ __align__(16) unsigned char inv_smem[];
+  int32_t* list = reinterpret_cast<int32_t*>(inv_smem);                 // [kInvEntries]
+  float* gcol = reinterpret_cast<float*>(list + kInvEntries);          // [kInvMaxQ]
+  int32_t* bin_start = reinterpret_cast<int32_t*>(gcol + kInvMaxQ);    // [kInvBins + 1]
+  int32_t* cursor = bin_start + kInvBins + 1;                          // [kInvBins]
+  int32_t* next_tok = cursor + kInvBins;                               // [1]
+
   const int dim = t.dim, Lq = t.q_slots, Nb = t.C;
-  const int d = blockIdx.x / max_chunks;
-  const int chunk = blockIdx.x - d * max_chunks;
+  const int d = blockIdx.x;
   const int d0 = __ldg(t.ib + d);
   const int Ld = __ldg(t.ib + d + 1) - d0;
-  const int tok0 = chunk * kSegTokens;
-  if (tok0 >= Ld) return;
-  const int ntok = min(kSegTokens, Ld - tok0);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const bool vec = vec_ok != 0;
-
-  for (int e = threadIdx.x; e < ntok * dim; e += kSegWarps * 32) seg_smem[e] = 0.f;
-  __syncthreads();
-
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int half = lane >> 4, hl = lane & 15;
   const T* Q = reinterpret_cast<const T*>(t.queries);
-  // entries (q, i) of this document, flattened: e = q*Lq + i.  Each warp takes
-  // 32 consecutive entries at a time; lane l inspects entry e0+l.
-  const int64_t n_entries = Nq * (int64_t)Lq;
-  for (int64_t e0 = (int64_t)warp * 32; e0 < n_entries; e0 += kSegWarps * 32) {
-    const int64_t e = e0 + lane;
-    int j = -1;
-    float gl = 0.f;
-    if (e < n_entries) {
-      const int64_t q = e / Lq;
-      const int i = (int)(e - q * Lq);
-      const int a = __ldg(argmax + (q * Nb + d) * (int64_t)Lq + i);
-      if (a >= tok0 && a < tok0 + ntok) {
-        j = a - tok0;
-        gl = __ldg(dscore + q * Nb + d);
-      }
-    }
-    unsigned hits = __ballot_sync(0xffffffffu, j >= 0);
-    while (hits) {
-      const int l = __ffs(hits) - 1;
-      hits &= hits - 1;
-      const int jj = __shfl_sync(0xffffffffu, j, l);
-      const float gv = __shfl_sync(0xffffffffu, gl, l);
-      const T* qrow = Q + (e0 + l) * dim;
-      float* dst = seg_smem + jj * dim;
-      for (int k = lane * 4; k < dim; k += 128) {
-        float qv[4];
-        load4<T>(qrow, vec, k, dim, qv);
+  int q_block = kInvEntries / Lq;
+  if (q_block > kInvMaxQ) q_block = kInvMaxQ;
+  if (q_block < 1) q_block = 1;  // the dispatcher guarantees Lq <= kInvEntries
+
+  for (int tok0 = blockIdx.y * kInvBins; tok0 < Ld; tok0 += gridDim.y * kInvBins) {
+    const int ntok = min(kInvBins, Ld - tok0);
+    for (int q0 = 0; q0 < Nq; q0 += q_block) {
+      const int nq = min(q_block, Nq - q0);
+      const int n_e = nq * Lq;
+      const int32_t* amax = argmax + ((int64_t)q0 * Nb + d) * Lq;  // entry (q, i) at amax[q*Nb*Lq + i]
+      __syncthreads();
+      for (int b = tid; b < ntok; b += kInvThreads) cursor[b] = 0;
+      for (int qq = tid; qq < nq; qq += kInvThreads) gcol[qq] = __ldg(dscore + (int64_t)(q0 + qq) * Nb + d);
+      if (tid == 0) *next_tok = 0;
+      __syncthreads();
+      // histogram of winning tokens
+      for (int e0 = tid; e0 < n_e; e0 += 4 * kInvThreads) {
+        int a[4];
 #pragma unroll
-        for (int x = 0; x < 4; ++x)
-          if (k + x < dim) atomicAdd(dst + k + x, gv * qv[x]);
+        for (int u = 0; u < 4; ++u) {  // four independent loads in flight
+          const int e = e0 + u * kInvThreads;
+          a[u] = -1;
+          if (e < n_e) {
+            const int qq = e / Lq, i = e - qq * Lq;
+            a[u] = __ldg(amax + (int64_t)qq * Nb * Lq + i) - tok0;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (a[u] >= 0 && a[u] < ntok) atomicAdd(&cursor[a[u]], 1);
+      }
+      __syncthreads();
+      // exclusive scan over the bins (one warp, contiguous slices per lane)
+      if (warp == 0) {
+        const int per = (ntok + 31) / 32;
+        const int b0 = lane * per, b1 = min(ntok, b0 + per);
+        int sum = 0;
+        for (int b = b0; b < b1; ++b) sum += cursor[b];
+        int incl = sum;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const int o = __shfl_up_sync(0xffffffffu, incl, off);
+          if (lane >= off) incl += o;
+        }
+        int run = incl - sum;
+        for (int b = b0; b < b1; ++b) {
+          const int c = cursor[b];
+          bin_start[b] = run;
+          cursor[b] = run;
+          run += c;
+        }
+        if (lane == 31) bin_start[ntok] = incl;
+      }
+      __syncthreads();
+      // scatter entry ids into their token's list
+      for (int e0 = tid; e0 < n_e; e0 += 4 * kInvThreads) {
+        int a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int e = e0 + u * kInvThreads;
+          a[u] = -1;
+          if (e < n_e) {
+            const int qq = e / Lq, i = e - qq * Lq;
+            a[u] = __ldg(amax + (int64_t)qq * Nb * Lq + i) - tok0;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (a[u] >= 0 && a[u] < ntok) list[atomicAdd(&cursor[a[u]], 1)] = e0 + u * kInvThreads;
+      }
+      __syncthreads();
+      // gather: warps claim tokens; each half-warp fetches one routed query row
+      for (;;) {
+        int j = 0;
+        if (lane == 0) j = atomicAdd(next_tok, 1);
+        j = __shfl_sync(0xffffffffu, j, 0);
+        if (j >= ntok) break;
+        const int beg = bin_start[j], end = bin_start[j + 1];
+        float* out = dd + ((int64_t)d0 + tok0 + j) * dim;
+        for (int kb = 0; kb < dim; kb += 128) {
+          const int k = kb + hl * 8;
+          const bool k_ok = k < dim;
+          float acc[8];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) acc[x] = 0.f;
+          constexpr int kFlight = sizeof(T) == 2 ? 8 : 4;  // rows in flight per lane
+          for (int p = beg; p < end; p += 2 * kFlight) {
+            Row8<T> rows[kFlight];
+            float gw[kFlight];
+#pragma unroll
+            for (int u = 0; u < kFlight; ++u) {
+              const int pp = p + 2 * u + half;
+              gw[u] = 0.f;
+              rows[u].zero();
+              if (pp < end && k_ok) {
+                const int e = list[pp];
+                gw[u] = gcol[e / Lq];
+                rows[u].load(Q + ((int64_t)q0 * Lq + e) * dim + k);
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < kFlight; ++u) rows[u].fma_into(gw[u], acc);
+          }
+#pragma unroll
+          for (int x = 0; x < 8; ++x) acc[x] += __shfl_xor_sync(0xffffffffu, acc[x], 16);
+          if (half == 0 && k_ok) {
+            float4* o4 = reinterpret_cast<float4*>(out + k);
+            if (q0 == 0) {
+              o4[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+              o4[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            } else {
+              float4 c0 = o4[0], c1 = o4[1];
+              o4[0] = make_float4(c0.x + acc[0], c0.y + acc[1], c0.z + acc[2], c0.w + acc[3]);
+              o4[1] = make_float4(c1.x + acc[4], c1.y + acc[5], c1.z + acc[6], c1.w + acc[7]);
+            }
+          }
+        }
       }
     }
   }
-  __syncthreads();
-  float* out = dd + ((int64_t)d0 + tok0) * dim;
-  for (int e = threadIdx.x; e < ntok * dim; e += kSegWarps * 32) out[e] = seg_smem[e];
 }
 
 }  // namespace maxsim

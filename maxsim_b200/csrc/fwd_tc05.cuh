@@ -101,8 +101,10 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
-  uint32_t r[32];
+// tcgen05.ld is asynchronous: its destination registers may only be read after
+// tcgen05.wait::ld.  The wait takes the registers as in/out operands so that
+// the compiler cannot schedule a use of them ahead of it.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -113,9 +115,73 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float (&v)[32]) {
         "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
         "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
+                 "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
+                 "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]),
+                 "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+                 "+r"(r[30]), "+r"(r[31])
+               :
+               : "memory");
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));  // NaN operands are ignored
+  return d;
+}
+
+// Maximum of 32 values with 3-input max instructions (16 instead of 31).
+__device__ __forceinline__ float max32(const float (&v)[32]) {
+  float t[11];
 #pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+  for (int i = 0; i < 10; ++i) t[i] = max3(v[3 * i], v[3 * i + 1], v[3 * i + 2]);
+  t[10] = fmaxf(v[30], v[31]);
+  const float a = max3(t[0], t[1], t[2]), b = max3(t[3], t[4], t[5]), c = max3(t[6], t[7], t[8]);
+  return max3(max3(a, b, c), t[9], t[10]);
+}
+
+// First index j in [0, 32) with v[j] == m, for a finite m that is the maximum
+// of v.  The search runs on the FMA pipe instead of compare/select pairs:
+// key_j = (v[j] - m) * 2^126 + c_j with c_j = 2^23 + (31 - j).  Where
+// v[j] == m the key is exactly c_j (larger for smaller j); elsewhere it is
+// hugely negative.  The maximum key therefore carries 31 - j* in its low
+// mantissa bits.  Returns -1 when no key is valid (m infinite or NaN), in which
+// case the caller falls back to a compare loop.
+__device__ __forceinline__ int first_index_of_max(const float (&v)[32], float m) {
+  const float kScale = 8.507059173023462e37f;  // 2^126
+  float key[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) key[j] = fmaf(v[j] - m, kScale, 8388608.0f + (float)(31 - j));
+  const float k = max32(key);
+  if (!(k >= 8388608.0f)) return -1;
+  return 31 - (__float_as_int(k) & 31);
+}
+
+// Folds 32 similarities of one document into the row's running maximum and
+// first-index argmax.  `base_ix` is the document-local index of column 0.
+template <bool ARGMAX>
+__device__ __forceinline__ void fold32(const float (&w)[32], int base_ix, float& run, int& idx) {
+  const float m = max32(w);
+  if (ARGMAX) {
+    if (__any_sync(0xffffffffu, m > run)) {
+      int first = first_index_of_max(w, m);
+      if (m > run) {
+        if (first < 0) {  // infinite maximum: compare loop
+          first = 31;
+#pragma unroll
+          for (int j = 30; j >= 0; --j) first = (w[j] == m) ? j : first;
+        }
+        run = m;
+        idx = base_ix + first;
+      }
+    }
+  } else {
+    run = fmaxf(run, m);
+  }
 }
 
 struct Params {
@@ -265,59 +331,62 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr0 =
             tmem_base + ((uint32_t)(quad * 32) << 16) + acc * (kMSub * kBN) + sub * kBN;
-#pragma unroll 1
+        // Chunks of 32 columns, the next chunk's TMEM load in flight while the
+        // current one is folded.
+        uint32_t raw[2][32];
+        const int tok_tile = s0 + tile * kBN;
+        int n_chunks = (min(s1 - tok_tile, kBN) + 31) >> 5;   // chunks that hold tokens of this item
+        if (d >= d_hi) n_chunks = 0;
+        if (n_chunks > 0) tmem_ld32_issue(taddr0, raw[0]);
+#pragma unroll
         for (int c4 = 0; c4 < kBN / 32; ++c4) {
-          const int tok0 = s0 + tile * kBN + c4 * 32;
-          if (tok0 >= s1 || d >= d_hi) break;  // uniform: nothing left in this item
-          float v[32];
-          tmem_ld32(taddr0 + c4 * 32, v);
-          int col = 0;
-          while (col < 32 && d < d_hi) {
-            const int seg_end = min(32, dend - tok0);
-            const int base_ix = tok0 - dstart;
-            if (col == 0 && seg_end == 32) {
-              float m = v[0];
+          if (c4 < n_chunks) {
+            tmem_ld_wait(raw[c4 & 1]);
+            if (c4 + 1 < n_chunks) tmem_ld32_issue(taddr0 + (c4 + 1) * 32, raw[(c4 + 1) & 1]);
+            float v[32];
 #pragma unroll
-              for (int j = 1; j < 32; ++j) m = fmaxf(m, v[j]);
-              if (ARGMAX) {
-                if (m > run) {
-                  run = m;
-                  int first = 31;
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c4 & 1][j]);
+            const int tok0 = tok_tile + c4 * 32;
+            int col = 0;
+            while (col < 32 && d < d_hi) {
+              const int seg_end = min(32, dend - tok0);
+              const int base_ix = tok0 - dstart;
+              // Columns of this chunk that belong to document d: [col, seg_end).
+              if (col == 0 && seg_end == 32) {
+                fold32<ARGMAX>(v, base_ix, run, idx);
+              } else if (ARGMAX) {
+                // boundary chunk: per-column predicated update (fewest instructions)
 #pragma unroll
-                  for (int j = 30; j >= 0; --j) first = (v[j] == m) ? j : first;
-                  idx = base_ix + first;
-                }
-              } else {
-                run = fmaxf(run, m);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (j >= col && j < seg_end) {
-                  if (ARGMAX) {
+                for (int j = 0; j < 32; ++j) {
+                  if (j >= col && j < seg_end) {
                     if (v[j] > run) { run = v[j]; idx = base_ix + j; }
-                  } else {
-                    run = fmaxf(run, v[j]);
                   }
                 }
-              }
-            }
-            col = max(col, seg_end);
-            if (tok0 + col >= dend) {
-              // document d complete for this warp's query
-              float sum = run;
+              } else {
+                float w[32];
+                const unsigned span = (unsigned)(seg_end - col);
 #pragma unroll
-              for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-              if (q_ok) {
-                const int64_t pair = (int64_t)q * P.Nb + d;
-                if (ARGMAX) P.argmax[pair * kLq + lane] = idx;
-                if (lane == 0) P.scores[pair] = sum;
+                for (int j = 0; j < 32; ++j)
+                  w[j] = ((unsigned)(j - col) < span) ? v[j] : neg_inf();
+                fold32<false>(w, base_ix, run, idx);
               }
-              run = neg_inf();
-              idx = 0;
-              ++d;
-              dstart = dend;
-              if (d < d_hi) dend = __ldg(doff + d + 1);
+              col = max(col, seg_end);
+              if (tok0 + col >= dend) {
+                // document d complete for this warp's query
+                float sum = run;
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+                if (q_ok) {
+                  const int64_t pair = (int64_t)q * P.Nb + d;
+                  if (ARGMAX) P.argmax[pair * kLq + lane] = idx;
+                  if (lane == 0) P.scores[pair] = sum;
+                }
+                run = neg_inf();
+                idx = 0;
+                ++d;
+                dstart = dend;
+                if (d < d_hi) dend = __ldg(doff + d + 1);
+              }
             }
           }
         }
