@@ -278,6 +278,54 @@ def bench_train_steps(dev, peaks, full: bool):
     return out
 
 
+def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
+    """Contrastive training step of the 1024 x 1024 ties configuration with
+    queries and documents sharded over the ranks: all-gather of the document
+    shards, local forward per source shard, cross-entropy on diagonal targets,
+    backward with per-owner reduction of grad_documents."""
+    from maxsim_b200 import dist as mdist
+    from maxsim_b200 import workloads as W
+
+    n = 256 if small else 1024
+    q0, q1 = mdist.shard_range(n, rank, world)
+    d0, d1 = mdist.shard_range(n, rank, world)
+    data = W.c5_device(dev, Nq=n, Nb=n, q_begin=q0, q_end=q1, d_begin=d0, d_end=d1)
+    q = data["queries"].requires_grad_(True)
+    d = data["documents"].requires_grad_(True)
+    lens = data["doc_lengths_all"][d0:d1].to(dev)
+    docs_per_rank = [mdist.shard_range(n, r, world)[1] - mdist.shard_range(n, r, world)[0]
+                     for r in range(world)]
+    target = mdist.contrastive_targets(q1 - q0, device=dev, docs_per_rank=docs_per_rank)
+
+    def step():
+        q.grad = None
+        d.grad = None
+        s = mdist.score_contrastive_sharded(q, d, lens)
+        torch.nn.functional.cross_entropy(s, target).backward()
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    iters = 10
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    T = int(data["doc_lengths_all"].sum().item())
+    flops = 2 * 128 * n * 32 * T + 4 * 128 * n * n * 32
+    return {"c5_contrastive_train_bf16_sharded": {
+        "ms_per_step": ms, "pairs_per_s": n * n / (ms * 1e-3),
+        "tensor_frac_all_gpus": flops / (ms * 1e-3) / (world * peaks["bf16_tflops"] * 1e12),
+        "note": f"global Nq=Nb={n} over {world} ranks (strong scaling); all-gather documents, "
+                "per-owner reduce of grad_documents; max over ranks"}}
+
+
 def run_contrastive_profile(args):
     """A few train steps of the contrastive-with-ties configuration, nothing
     else: the command a profiler wraps."""
@@ -420,12 +468,14 @@ def run_gpu_arm(args):
 
     train = None
     cpu_base = None
-    if rank == 0 and world == 1:
-        del documents, d_flat, data
-        torch.cuda.empty_cache()
+    del documents, d_flat, data
+    torch.cuda.empty_cache()
+    if world == 1:
         train = bench_train_steps(dev, peaks, full=not args.small)
         v, cores, sample = cpu_padded_baseline(target_seconds=2.0 if args.small else 12.0)
         cpu_base = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+    else:
+        train = bench_sharded_train_step(dev, dist, rank, world, peaks, small=args.small)
 
     if rank == 0:
         value = world * pairs * args.steps / (elapsed_ms * 1e-3)

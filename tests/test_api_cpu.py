@@ -179,3 +179,33 @@ def test_ops_namespace_matches_reference_operator_names():
         "maxsim_contrastive_backward",
     }
     assert expected == set(vars(_ops.ops))
+
+
+def test_reference_python_layer_runs_on_this_ops_namespace():
+    """The reference's own maxsim/__init__.py imports and dispatches into this
+    package's operator namespace when it is installed as maxsim._ops (the seam
+    described in INTEGRATION.md).  Needs the reference checkout."""
+    import importlib
+    import sys
+    import types
+
+    ref = Path("/root/reference/torch-ext")
+    if not (ref / "maxsim" / "__init__.py").exists():
+        pytest.skip("reference checkout not present")
+    saved = {k: sys.modules.pop(k) for k in list(sys.modules) if k == "maxsim" or k.startswith("maxsim.")}
+    shim = types.ModuleType("maxsim._ops")
+    shim.ops = _ops.ops
+    sys.modules["maxsim._ops"] = shim
+    sys.path.insert(0, str(ref))
+    try:
+        ref_maxsim = importlib.import_module("maxsim")
+        for name in ("score_pairs_packed", "score_candidates_padded_train", "score_contrastive_with_argmax"):
+            assert hasattr(ref_maxsim, name)
+        q, d, qlen, dlen = _padded()
+        with pytest.raises(RuntimeError, match="CUDA"):  # reached our operator, which has no CPU path
+            ref_maxsim.score_candidates_padded(q, d, qlen, dlen)
+    finally:
+        sys.path.remove(str(ref))
+        for k in [k for k in sys.modules if k == "maxsim" or k.startswith("maxsim.")]:
+            del sys.modules[k]
+        sys.modules.update(saved)

@@ -1,0 +1,85 @@
+"""The multi-GPU drivers on real devices (NCCL, one process per GPU): sharded
+contrastive training and query-sharded rerank against the same computation on a
+single GPU.  Skipped when fewer than two GPUs are visible."""
+
+from __future__ import annotations
+
+import os
+import socket
+import sys
+from datetime import timedelta
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    sys.path.insert(0, str(ROOT))
+    import torch.distributed as dist
+    import maxsim_b200 as maxsim
+    from maxsim_b200 import dist as mdist, workloads as W
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            timeout=timedelta(seconds=120))
+    try:
+        n = 96
+        full = W.c5_device(dev, Nq=n, Nb=n, lo=16, hi=200)
+        q0, q1 = mdist.shard_range(n, rank, world)
+        d0, d1 = mdist.shard_range(n, rank, world)
+        part = W.c5_device(dev, Nq=n, Nb=n, lo=16, hi=200, q_begin=q0, q_end=q1, d_begin=d0, d_end=d1)
+        off = full["document_offsets"]
+        assert torch.equal(part["queries"], full["queries"][q0:q1])
+        assert torch.equal(part["documents"], full["documents"][int(off[d0]):int(off[d1])])
+        q = part["queries"].clone().requires_grad_(True)
+        d = part["documents"].clone().requires_grad_(True)
+        lens = full["doc_lengths_all"][d0:d1].to(dev)
+        s = mdist.score_contrastive_sharded(q, d, lens)
+        g = torch.randn(n, n, generator=torch.Generator().manual_seed(3)).to(dev)
+        (s * g[q0:q1]).sum().backward()
+        # the same thing on this GPU alone
+        qf = full["queries"].clone().requires_grad_(True)
+        df = full["documents"].clone().requires_grad_(True)
+        sf = maxsim.score_contrastive_train(qf, df, off)
+        (sf * g).sum().backward()
+        torch.testing.assert_close(s, sf[q0:q1], rtol=1e-5, atol=1e-5)
+        torch.testing.assert_close(q.grad.float(), qf.grad[q0:q1].float(), rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(d.grad.float(), df.grad[int(off[d0]):int(off[d1])].float(),
+                                   rtol=2e-2, atol=2e-2)
+        # rerank shard
+        wl = W.c3_device_shard(rank * 3, rank * 3 + 3, dev, C=40)
+        local = mdist.score_candidates_padded_sharded(wl["queries"], wl["documents"],
+                                                      wl["query_lengths"], wl["doc_lengths"])
+        gathered = mdist.score_candidates_padded_sharded(wl["queries"], wl["documents"],
+                                                         wl["query_lengths"], wl["doc_lengths"],
+                                                         gather=True)
+        assert gathered.shape == (3 * world, 40)
+        assert torch.equal(gathered[rank * 3:(rank + 1) * 3], local)
+        Path(out_dir, f"ok{rank}").write_text("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_drivers_match_single_gpu(tmp_path):
+    world = min(torch.cuda.device_count(), 4)
+    if world < 2:
+        pytest.skip("needs at least two GPUs")
+    import torch.multiprocessing as mp
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    assert all((tmp_path / f"ok{r}").exists() for r in range(world))
