@@ -451,6 +451,8 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
       }
       __syncthreads();
       // gather: warps claim tokens; each half-warp fetches one routed query row
+      const int lq_shift = (Lq & (Lq - 1)) == 0 ? (31 - __clz(Lq)) : -1;  // Lq a power of two
+      const T* qpass = Q + (int64_t)q0 * Lq * dim;
       for (;;) {
         int j = 0;
         if (lane == 0) j = atomicAdd(next_tok, 1);
@@ -461,26 +463,34 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
         for (int kb = 0; kb < dim; kb += 128) {
           const int k = kb + hl * 8;
           const bool k_ok = k < dim;
+          const T* qk = qpass + k;
           float acc[8];
 #pragma unroll
           for (int x = 0; x < 8; ++x) acc[x] = 0.f;
           constexpr int kFlight = sizeof(T) == 2 ? 8 : 4;  // rows in flight per lane
-          for (int p = beg; p < end; p += 2 * kFlight) {
-            Row8<T> rows[kFlight];
-            float gw[kFlight];
+          int p = beg + half;
+          if (k_ok) {
+            // full groups: no bounds checks
+            for (; p + 2 * (kFlight - 1) < end; p += 2 * kFlight) {
+              Row8<T> rows[kFlight];
+              float gw[kFlight];
 #pragma unroll
-            for (int u = 0; u < kFlight; ++u) {
-              const int pp = p + 2 * u + half;
-              gw[u] = 0.f;
-              rows[u].zero();
-              if (pp < end && k_ok) {
-                const int e = list[pp];
-                gw[u] = gcol[e / Lq];
-                rows[u].load(Q + ((int64_t)q0 * Lq + e) * dim + k);
+              for (int u = 0; u < kFlight; ++u) {
+                const int e = list[p + 2 * u];
+                gw[u] = gcol[lq_shift >= 0 ? (e >> lq_shift) : (e / Lq)];
+                rows[u].load(qk + (int64_t)e * dim);
               }
-            }
 #pragma unroll
-            for (int u = 0; u < kFlight; ++u) rows[u].fma_into(gw[u], acc);
+              for (int u = 0; u < kFlight; ++u) rows[u].fma_into(gw[u], acc);
+            }
+            // tail
+            for (; p < end; p += 2) {
+              const int e = list[p];
+              const float g1 = gcol[lq_shift >= 0 ? (e >> lq_shift) : (e / Lq)];
+              Row8<T> r;
+              r.load(qk + (int64_t)e * dim);
+              r.fma_into(g1, acc);
+            }
           }
 #pragma unroll
           for (int x = 0; x < 8; ++x) acc[x] += __shfl_xor_sync(0xffffffffu, acc[x], 16);
