@@ -32,25 +32,39 @@
 namespace maxsim {
 namespace tc05 {
 
-constexpr int kBM = 128;   // rows per accumulator
-constexpr int kMSub = 2;   // accumulators per CTA
+constexpr int kBM = 128;   // rows per accumulator (TMEM lanes)
 constexpr int kLq = 32;
-constexpr int kQPerSub = kBM / kLq;          // 4 queries per accumulator
-constexpr int kQPerCta = kQPerSub * kMSub;   // 8
-constexpr int kBN = 128;   // document tokens per tile
+constexpr int kQPerSub = kBM / kLq;  // 4 queries per accumulator
 constexpr int kDim = 128;
-constexpr int kBStages = 4;
 constexpr int kAccStages = 2;
-constexpr int kEpiWarps = 4 * kMSub;
-constexpr int kThreads = 64 + 32 * kEpiWarps;
-constexpr int kTmemCols = kMSub * kBN * kAccStages;  // 512
-constexpr int kHalfBytes = kBM * 128;                // one 128-row x 64-element box: 16 KB
-constexpr int kTileBytes = 2 * kHalfBytes;           // 32 KB
+constexpr int kABoxBytes = kBM * 128;  // one 128-row x 64-element box of the query block: 16 KB
 constexpr uint32_t kWaitLimit = 1u << 22;
 
-constexpr size_t kSmemA = (size_t)kMSub * kTileBytes;
-constexpr size_t kSmemB = (size_t)kBStages * kTileBytes;
-constexpr size_t kSmemBytes = kSmemA + kSmemB + 1024 /*alignment slack*/ + 256 /*barriers*/;
+// A kernel configuration: MSUB accumulators of 128 rows per CTA (M = 128*MSUB)
+// and document tiles of BN tokens.  TMEM holds MSUB*BN*2 columns (<= 512).
+//   <2, 128>: M = 256,  8 epilogue warps, each folds 128 columns per tile
+//   <4,  64>: M = 512, 16 epilogue warps, each folds  64 columns per tile; four
+//             warps per scheduler hide the epilogue's dependent-issue latency
+//             and every staged document tile is used by twice as many queries.
+template <int MSUB, int BN>
+struct Cfg {
+  static constexpr int kMSub = MSUB;
+  static constexpr int kBN = BN;
+  static constexpr int kQPerCta = kQPerSub * MSUB;
+  static constexpr int kEpiWarps = 4 * MSUB;
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static constexpr int kTmemCols = MSUB * BN * kAccStages;
+  static constexpr int kBBoxBytes = BN * 128;          // one BN-row x 64-element box
+  static constexpr int kBTileBytes = 2 * kBBoxBytes;
+  static constexpr int kATileBytes = 2 * kABoxBytes;   // 32 KB per accumulator
+  static constexpr int kBStages = 4;
+  static constexpr size_t kSmemA = (size_t)MSUB * kATileBytes;
+  static constexpr size_t kSmemB = (size_t)kBStages * kBTileBytes;
+  static constexpr size_t kSmemBytes = kSmemA + kSmemB + 1024 /*alignment slack*/ + 256 /*barriers*/;
+  static constexpr bool kPrefetch = (MSUB <= 2);  // second TMEM register buffer only if registers allow
+  static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
+  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile tokens");
+};
 
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity) {
   for (uint32_t it = 0; it < kWaitLimit; ++it) {
@@ -189,16 +203,21 @@ struct Params {
   float* scores;
   int32_t* argmax;
   int32_t Nq, Nb;
-  int32_t n_qgroups;      // ceil(Nq / 8)
+  int32_t n_qgroups;      // ceil(Nq / queries per CTA)
   int32_t docs_per_item;
-  int32_t n_items;
+  int32_t n_items;        // document runs x query groups, query group fastest
   uint32_t idesc;
 };
 
-template <bool ARGMAX>
-__global__ void __launch_bounds__(kThreads, 1)
+template <bool ARGMAX, int MSUB, int BN>
+__global__ void __launch_bounds__(Cfg<MSUB, BN>::kThreads, 1)
 fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_d,
                 const Params P) {
+  using C = Cfg<MSUB, BN>;
+  constexpr int kMSub = C::kMSub, kBN = C::kBN, kBStages = C::kBStages, kEpiWarps = C::kEpiWarps;
+  constexpr int kTmemCols = C::kTmemCols, kQPerCta = C::kQPerCta;
+  constexpr size_t kSmemA = C::kSmemA, kSmemB = C::kSmemB;
+  (void)kQPerCta;
   extern __shared__ unsigned char tc05_smem_raw[];
   const uint32_t raw = smem_u32(tc05_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -240,6 +259,10 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(tmem_slot));
 
   const int32_t* __restrict__ doff = P.doc_offsets;
+  // Items are dealt round-robin with the query group varying fastest, so the
+  // CTAs running at any moment work on the same run of documents and share its
+  // tiles through L2.  (Giving each CTA a contiguous range of items to spare
+  // query-block reloads measured slower.)
 
   if (warp == 0) {
     // ===================== TMA producer ====================================
@@ -257,15 +280,15 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int sub = 0; sub < kMSub; ++sub)
 #pragma unroll
           for (int h = 0; h < 2; ++h)
-            tma_load_2d(smA + sub * kTileBytes + h * kHalfBytes, &tm_q, h * 64,
+            tma_load_2d(smA + sub * C::kATileBytes + h * kABoxBytes, &tm_q, h * 64,
                         (qg * kMSub + sub) * kBM, a_full);
         for (int tile = 0; tile < ntiles; ++tile) {
           if (!wait_bounded(b_empty + 8 * bs, bph ^ 1u)) { ok = false; break; }
-          mbar_expect_tx(b_full + 8 * bs, (uint32_t)kTileBytes);
+          mbar_expect_tx(b_full + 8 * bs, (uint32_t)C::kBTileBytes);
 #pragma unroll
           for (int h = 0; h < 2; ++h)
-            tma_load_2d(smB + bs * kTileBytes + h * kHalfBytes, &tm_d, h * 64, s0 + tile * kBN,
-                        b_full + 8 * bs);
+            tma_load_2d(smB + bs * C::kBTileBytes + h * C::kBBoxBytes, &tm_d, h * 64,
+                        s0 + tile * kBN, b_full + 8 * bs);
           if (++bs == kBStages) { bs = 0; bph ^= 1u; }
         }
       }
@@ -291,9 +314,10 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const uint32_t d_tmem = tmem_base + acc * (kMSub * kBN) + sub * kBN;
 #pragma unroll
             for (int k = 0; k < kDim / 16; ++k) {
-              const uint32_t koff = (k >> 2) * kHalfBytes + (k & 3) * 32;
-              const uint64_t ad = umma_desc(smA + sub * kTileBytes + koff);
-              const uint64_t bd = umma_desc(smB + bs * kTileBytes + koff);
+              const uint64_t ad =
+                  umma_desc(smA + sub * C::kATileBytes + (k >> 2) * kABoxBytes + (k & 3) * 32);
+              const uint64_t bd =
+                  umma_desc(smB + bs * C::kBTileBytes + (k >> 2) * C::kBBoxBytes + (k & 3) * 32);
               umma_f16(d_tmem, ad, bd, P.idesc, k > 0 ? 1u : 0u);
             }
           }
@@ -333,19 +357,24 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tmem_base + ((uint32_t)(quad * 32) << 16) + acc * (kMSub * kBN) + sub * kBN;
         // Chunks of 32 columns, the next chunk's TMEM load in flight while the
         // current one is folded.
-        uint32_t raw[2][32];
+        constexpr int kBufs = C::kPrefetch ? 2 : 1;
+        uint32_t raw[kBufs][32];
         const int tok_tile = s0 + tile * kBN;
         int n_chunks = (min(s1 - tok_tile, kBN) + 31) >> 5;   // chunks that hold tokens of this item
         if (d >= d_hi) n_chunks = 0;
-        if (n_chunks > 0) tmem_ld32_issue(taddr0, raw[0]);
+        if (C::kPrefetch && n_chunks > 0) tmem_ld32_issue(taddr0, raw[0]);
 #pragma unroll
         for (int c4 = 0; c4 < kBN / 32; ++c4) {
           if (c4 < n_chunks) {
-            tmem_ld_wait(raw[c4 & 1]);
-            if (c4 + 1 < n_chunks) tmem_ld32_issue(taddr0 + (c4 + 1) * 32, raw[(c4 + 1) & 1]);
+            constexpr int kNoBuf = 0;
+            const int cur = C::kPrefetch ? (c4 & 1) : kNoBuf;
+            if (!C::kPrefetch) tmem_ld32_issue(taddr0 + c4 * 32, raw[0]);
+            tmem_ld_wait(raw[cur]);
+            if (C::kPrefetch && c4 + 1 < n_chunks)
+              tmem_ld32_issue(taddr0 + (c4 + 1) * 32, raw[(c4 + 1) & (kBufs - 1)]);
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[c4 & 1][j]);
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[cur][j]);
             const int tok0 = tok_tile + c4 * 32;
             int col = 0;
             while (col < 32 && d < d_hi) {
@@ -433,12 +462,12 @@ inline TensorMapEncodeFn tensor_map_encoder() {
 }
 
 // rows x 128 row-major matrix of 16-bit elements, boxes of 128 rows x 64 elements
-inline bool encode_rows128(CUtensorMap* map, const void* base, int64_t rows, bool bf16) {
+inline bool encode_rows128(CUtensorMap* map, const void* base, int64_t rows, int box_rows, bool bf16) {
   TensorMapEncodeFn enc = tensor_map_encoder();
   if (!enc || rows <= 0) return false;
   cuuint64_t gdim[2] = {(cuuint64_t)tc05::kDim, (cuuint64_t)rows};
   cuuint64_t gstride[1] = {(cuuint64_t)tc05::kDim * 2};
-  cuuint32_t box[2] = {64, (cuuint32_t)tc05::kBM};
+  cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = enc(map, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                    const_cast<void*>(base), gdim, gstride, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -453,21 +482,22 @@ inline bool tc05_eligible(const PairTable& t, int dtype) {
   if ((reinterpret_cast<uintptr_t>(t.queries) & 15u) || (reinterpret_cast<uintptr_t>(t.documents) & 15u))
     return false;
   const int64_t Nb = t.C, Nq = t.n_pairs / (Nb > 0 ? Nb : 1);
-  if (Nq < tc05::kQPerCta || Nb < 1) return false;
+  if (Nq < 8 || Nb < 1) return false;
   if (t.d_rows <= 0 || t.d_rows >= (1ll << 31) || Nq * tc05::kLq >= (1ll << 31)) return false;
   return tensor_map_encoder() != nullptr;
 }
 
 // Returns 0 on success, 1 if the launch could not be prepared (caller falls
 // back to another kernel), or a CUDA error code < 0.
-template <bool ARGMAX>
-int launch_tc05(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
-                cudaStream_t st) {
+template <bool ARGMAX, int MSUB, int BN>
+int launch_tc05_cfg(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
+                    cudaStream_t st) {
+  using C = tc05::Cfg<MSUB, BN>;
   const int64_t Nb = t.C, Nq = t.n_pairs / Nb;
   CUtensorMap tm_q, tm_d;
   const bool bf16 = dtype == 2;
-  if (!encode_rows128(&tm_q, t.queries, Nq * tc05::kLq, bf16)) return 1;
-  if (!encode_rows128(&tm_d, t.documents, t.d_rows, bf16)) return 1;
+  if (!encode_rows128(&tm_q, t.queries, Nq * tc05::kLq, tc05::kBM, bf16)) return 1;
+  if (!encode_rows128(&tm_d, t.documents, t.d_rows, BN, bf16)) return 1;
 
   tc05::Params P;
   P.doc_offsets = t.ib;
@@ -475,7 +505,7 @@ int launch_tc05(const PairTable& t, float* scores, int32_t* argmax, int dtype, i
   P.argmax = argmax;
   P.Nq = (int32_t)Nq;
   P.Nb = (int32_t)Nb;
-  P.n_qgroups = (int32_t)((Nq + tc05::kQPerCta - 1) / tc05::kQPerCta);
+  P.n_qgroups = (int32_t)((Nq + C::kQPerCta - 1) / C::kQPerCta);
   int64_t dpi = (Nb * (int64_t)P.n_qgroups) / (16ll * sms);
   if (dpi < 1) dpi = 1;
   if (dpi > Nb) dpi = Nb;
@@ -485,22 +515,30 @@ int launch_tc05(const PairTable& t, float* scores, int32_t* argmax, int dtype, i
   if (n_items >= (1ll << 31)) return 1;
   P.n_items = (int32_t)n_items;
   const uint32_t fmt = bf16 ? 1u : 0u;
-  P.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(tc05::kBN >> 3) << 17) |
+  P.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) |
             ((uint32_t)(tc05::kBM >> 4) << 24);
 
-  auto kern = tc05::fwd_tc05_kernel<ARGMAX>;
+  auto kern = tc05::fwd_tc05_kernel<ARGMAX, MSUB, BN>;
   static bool configured[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -3;
   if (dev < 0 || dev >= 64 || !configured[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)tc05::kSmemBytes) != cudaSuccess)
+                             (int)C::kSmemBytes) != cudaSuccess)
       return -3;
     if (dev >= 0 && dev < 64) configured[dev] = true;
   }
   const int grid = (int)(n_items < sms ? n_items : sms);
-  kern<<<grid, tc05::kThreads, tc05::kSmemBytes, st>>>(tm_q, tm_d, P);
+  kern<<<grid, C::kThreads, C::kSmemBytes, st>>>(tm_q, tm_d, P);
   return 0;
+}
+
+// `wide` selects the M = 512 configuration (16 queries per CTA).
+template <bool ARGMAX>
+int launch_tc05(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
+                cudaStream_t st, bool wide) {
+  if (wide) return launch_tc05_cfg<ARGMAX, 4, 64>(t, scores, argmax, dtype, sms, st);
+  return launch_tc05_cfg<ARGMAX, 2, 128>(t, scores, argmax, dtype, sms, st);
 }
 
 }  // namespace maxsim

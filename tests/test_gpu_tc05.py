@@ -56,7 +56,9 @@ SHAPES = [
 
 @pytest.mark.parametrize("Nq,d_lens", SHAPES)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_tc05_matches_oracle(Nq, d_lens, dtype):
+@pytest.mark.parametrize("path", [3, 4])  # 3: configuration chosen by Nq, 4: M = 256 forced
+def test_tc05_matches_oracle(Nq, d_lens, dtype, path):
+    _ops.set_forward_path(path)
     q, d, off = _make(Nq, d_lens, dtype, 11)
     _check(q, d, off, dtype)
 
