@@ -74,6 +74,17 @@ MAXSIM_API int64_t maxsim_b200_launch_count(void);
  * query count), 4 = force its M = 256 configuration.  For tests and profiling. */
 MAXSIM_API void maxsim_b200_set_forward_path(int path);
 
+/* Host-side validation helper (no reference counterpart: the reference copies
+ * whole offset / id tensors to the host, torch-ext/maxsim/__init__.py:184-223).
+ * Reduces a CSR offsets array and/or an id array (either may be NULL with
+ * count 0; elements are int32 when index_bytes == 4, int64 when 8) to eight
+ * int64 values written to device memory out8: offsets[0], offsets[n-1],
+ * smallest segment, largest segment, smallest id, largest id, n_offsets,
+ * n_ids. */
+MAXSIM_API int maxsim_b200_layout_stats(const void* offsets, int64_t n_offsets,
+                                        const void* ids, int64_t n_ids,
+                                        int index_bytes, int64_t* out8, void* stream);
+
 /* ------------------------------------------------------------------------
  * Packed pair grids.
  * queries [total_q_tokens, dim], query_offsets [n_queries+1],

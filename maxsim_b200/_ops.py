@@ -37,6 +37,7 @@ _SIGNATURES = {
     "maxsim_b200_device_status": (c_int, [_P]),
     "maxsim_b200_launch_count": (c_int64, []),
     "maxsim_b200_set_forward_path": (None, [c_int]),
+    "maxsim_b200_layout_stats": (c_int, [_P, _I64, _P, _I64, c_int, _P, _P]),
     "maxsim_forward": (c_int, [_P] * 7 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_forward_with_argmax": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_backward": (c_int, [_P] * 10 + [_I64] * 7 + [c_int, _P]),
@@ -91,6 +92,32 @@ def device_status(device=None) -> int:
     """Synchronise the current stream and return the kernels' status word."""
     with torch.cuda.device(device):
         return int(load_library().maxsim_b200_device_status(_stream_ptr()))
+
+
+def layout_stats(items) -> list:
+    """``items``: list of ``(offsets or None, ids or None)`` index tensors on
+    one CUDA device (each pair shares a dtype, int32 or int64).  Returns one
+    list of eight ints per item -- first offset, last offset, smallest and
+    largest segment, smallest and largest id, counts -- using one small kernel
+    per item and a single device-to-host transfer for all of them."""
+    lib = load_library()
+    dev = next(t for pair in items for t in pair if t is not None).device
+    out = torch.empty((len(items), 8), dtype=torch.int64, device=dev)
+    keep = []
+    with torch.cuda.device(dev):
+        for row, (offsets, ids) in enumerate(items):
+            ref = offsets if offsets is not None else ids
+            o = offsets.detach().reshape(-1).contiguous() if offsets is not None else None
+            i = ids.detach().reshape(-1).contiguous() if ids is not None else None
+            if i is not None and o is not None and i.dtype != o.dtype:
+                i = i.to(o.dtype)
+            keep.append((o, i))
+            rc = lib.maxsim_b200_layout_stats(
+                _ptr(o) if o is not None else 0, o.numel() if o is not None else 0,
+                _ptr(i) if i is not None else 0, i.numel() if i is not None else 0,
+                ref.element_size(), out[row].data_ptr(), _stream_ptr())
+            _check(rc, "maxsim_b200_layout_stats")
+    return out.tolist()
 
 
 def _stream_ptr() -> int:

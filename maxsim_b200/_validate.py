@@ -14,7 +14,8 @@ tensor inspected element by element to name the offending index.
 
 from __future__ import annotations
 
-from typing import Dict, Tuple
+import weakref
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -49,13 +50,75 @@ def _host_ints(*scalars: torch.Tensor) -> list:
 
 
 # ---------------------------------------------------------------------------
+# Index-tensor statistics: one small device kernel per tensor, one transfer per
+# call, and nothing at all for a tensor object that was already inspected and
+# has not been written since (same Python object, same version counter).
+# ---------------------------------------------------------------------------
+
+_STATS_CACHE: Dict[int, tuple] = {}
+_STATS_CACHE_LIMIT = 64
+
+
+def _cache_get(t: torch.Tensor) -> Optional[tuple]:
+    ent = _STATS_CACHE.get(id(t))
+    if ent is not None and ent[0]() is t and ent[1] == t._version:
+        return ent[2]
+    return None
+
+
+def _cache_put(t: torch.Tensor, stats: tuple) -> None:
+    if len(_STATS_CACHE) >= _STATS_CACHE_LIMIT:
+        _STATS_CACHE.clear()
+    try:
+        _STATS_CACHE[id(t)] = (weakref.ref(t), t._version, stats)
+    except TypeError:
+        pass
+
+
+def _torch_stats(t: torch.Tensor, as_offsets: bool) -> tuple:
+    flat = t.detach().reshape(-1).to(torch.int64)
+    if as_offsets:
+        seg = flat[1:] - flat[:-1]
+        return tuple(_host_ints(flat[0], flat[-1], seg.min(), seg.max()))
+    if flat.numel() == 0:
+        return (0, 0)
+    return tuple(_host_ints(flat.min(), flat.max()))
+
+
+def index_stats(offsets=(), ids=()):
+    """Statistics of CSR offset tensors -> ``(first, last, min_seg, max_seg)``
+    and of id / length tensors -> ``(min, max)``, in argument order.  Offsets
+    tensors need at least two elements; empty id tensors give ``(0, 0)``."""
+    results: Dict[int, tuple] = {}
+    todo = []
+    for t, is_off in [(t, True) for t in offsets] + [(t, False) for t in ids]:
+        hit = _cache_get(t)
+        if hit is not None and len(hit) == (4 if is_off else 2):
+            results[id(t)] = hit
+        else:
+            todo.append((t, is_off))
+    cuda = [x for x in todo if x[0].device.type == "cuda" and x[0].numel() > 0]
+    if cuda:
+        from . import _ops
+        rows = _ops.layout_stats([(t, None) if is_off else (None, t) for t, is_off in cuda])
+        for (t, is_off), row in zip(cuda, rows):
+            results[id(t)] = tuple(row[0:4]) if is_off else tuple(row[4:6])
+    for t, is_off in todo:
+        if id(t) not in results:
+            results[id(t)] = _torch_stats(t, is_off)
+    for t, _ in todo:
+        _cache_put(t, results[id(t)])
+    return [results[id(t)] for t in offsets], [results[id(t)] for t in ids]
+
+
+# ---------------------------------------------------------------------------
 # Padded layout
 # ---------------------------------------------------------------------------
 
-def _length_bounds(lengths: torch.Tensor, limit: int, name: str) -> None:
-    if lengths.numel() == 0:
+def _length_bounds(stats: tuple, numel: int, limit: int, name: str) -> None:
+    if numel == 0:
         return
-    lo, hi = _host_ints(lengths.min(), lengths.max())
+    lo, hi = stats
     if lo <= 0:
         raise ValueError(f"{name} must contain values > 0")
     if hi > limit:
@@ -88,8 +151,9 @@ def check_padded(queries, documents, query_lengths, doc_lengths) -> Tuple[int, i
     require_index("doc_lengths", doc_lengths)
     require_same_device(dict(queries=queries, documents=documents,
                              query_lengths=query_lengths, doc_lengths=doc_lengths))
-    _length_bounds(query_lengths, Lq_max, "query_lengths")
-    _length_bounds(doc_lengths, Ld_max, "doc_lengths")
+    _, (qs, ds) = index_stats(ids=(query_lengths, doc_lengths))
+    _length_bounds(qs, query_lengths.numel(), Lq_max, "query_lengths")
+    _length_bounds(ds, doc_lengths.numel(), Ld_max, "doc_lengths")
     return B, C, Lq_max, Ld_max, D
 
 
@@ -136,20 +200,6 @@ def check_packed_types(queries, query_offsets, documents, document_offsets,
         raise ValueError(f"pair_query_ids must be 1-D; got shape {tuple(pair_query_ids.shape)}")
 
 
-def _offset_stats(offsets: torch.Tensor):
-    o = offsets.detach().reshape(-1).to(torch.int64)
-    seg = o[1:] - o[:-1]
-    return [o[0], o[-1], seg.min(), seg.max()]
-
-
-def _id_stats(ids: torch.Tensor):
-    i = ids.detach().reshape(-1)
-    if i.numel() == 0:
-        z = torch.zeros((), dtype=torch.int64, device=ids.device)
-        return [z, z]
-    return [i.min(), i.max()]
-
-
 def _first_index(mask: torch.Tensor) -> int:
     return int(torch.nonzero(mask.reshape(-1))[0].item())
 
@@ -162,9 +212,12 @@ def check_packed_layout(queries, query_offsets, documents, document_offsets,
     for name, off in (("query_offsets", query_offsets), ("document_offsets", document_offsets)):
         if off.numel() < 2:
             raise RuntimeError(f"{name} must have length >= 2")
-    q0, qN, qmin, qmax, d0, dN, dmin, _dmax, qid_lo, qid_hi, did_lo, did_hi = _host_ints(
-        *_offset_stats(query_offsets), *_offset_stats(document_offsets),
-        *_id_stats(pair_query_ids), *_id_stats(pair_document_ids))
+    (qo, do), (qi, di) = index_stats(offsets=(query_offsets, document_offsets),
+                                     ids=(pair_query_ids, pair_document_ids))
+    q0, qN, qmin, qmax = qo
+    d0, dN, dmin, _dmax = do
+    qid_lo, qid_hi = qi
+    did_lo, did_hi = di
 
     def offsets_ok(name, off, first, last, smallest, total):
         if first != 0:
@@ -234,7 +287,7 @@ def check_contrastive(queries, documents, document_offsets) -> None:
                          f"got {document_offsets.numel()}")
     require_same_device(dict(queries=queries, documents=documents,
                              document_offsets=document_offsets))
-    first, last, smallest, _ = _host_ints(*_offset_stats(document_offsets))
+    ((first, last, smallest, _),), _ = index_stats(offsets=(document_offsets,))
     total = documents.shape[0]
     if first != 0:
         raise ValueError("document_offsets[0] must equal 0 (CSR offset convention); "

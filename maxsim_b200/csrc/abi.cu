@@ -12,6 +12,7 @@
 #include "fwd_mma.cuh"
 #include "fwd_simt.cuh"
 #include "fwd_tc05.cuh"
+#include "layout_stats.cuh"
 
 namespace maxsim {
 
@@ -305,6 +306,22 @@ int maxsim_b200_device_status(void* stream) {
   if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return MAXSIM_ECUDA;
   if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
   return v;
+}
+
+int maxsim_b200_layout_stats(const void* offsets, int64_t n_offsets, const void* ids, int64_t n_ids,
+                             int index_bytes, int64_t* out8, void* stream) {
+  if (!out8) return fail(MAXSIM_EINVAL, "null output pointer");
+  if ((n_offsets > 0 && !offsets) || (n_ids > 0 && !ids) || n_offsets < 0 || n_ids < 0)
+    return fail(MAXSIM_EINVAL, "null index array");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  long long* out = reinterpret_cast<long long*>(out8);
+  if (index_bytes == 4)
+    layout_stats_kernel<int32_t><<<1, kStatsThreads, 0, st>>>(offsets, n_offsets, ids, n_ids, out);
+  else if (index_bytes == 8)
+    layout_stats_kernel<int64_t><<<1, kStatsThreads, 0, st>>>(offsets, n_offsets, ids, n_ids, out);
+  else
+    return fail(MAXSIM_EINVAL, "index_bytes must be 4 or 8");
+  return launch_check("layout_stats_kernel");
 }
 
 int maxsim_forward(const void* queries, const int32_t* query_offsets, const void* documents,
