@@ -337,8 +337,9 @@ def bench_train_steps(dev, peaks, full: bool):
 def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
     """Contrastive training step of the 1024 x 1024 ties configuration with
     queries and documents sharded over the ranks: all-gather of the document
-    shards, local forward per source shard, cross-entropy on diagonal targets,
-    backward with per-owner reduction of grad_documents."""
+    shards, one forward launch over the gathered buffer, cross-entropy on
+    diagonal targets, one backward launch and a reduce-scatter of
+    grad_documents."""
     from maxsim_b200 import dist as mdist
     from maxsim_b200 import workloads as W
 

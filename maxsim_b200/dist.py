@@ -11,15 +11,17 @@ Rerank (padded / packed candidates)
 
 Contrastive training
     Rank r owns ``Nq/R`` queries and ``Nb/R`` documents.  Forward: the packed
-    document shards are all-gathered (they are ragged, so each is padded to the
-    longest shard for the collective and never compacted afterwards); the rank
-    scores its queries against one source shard at a time, starting with its
-    own shard while the gather is still in flight.  Backward: for every owner
-    rank the partial ``grad_documents`` of that owner's shard is reduced to the
-    owner as soon as the chunk is computed, overlapping with the next chunk;
-    ``grad_queries`` stays local.  Scores come back as ``[Nq_local, Nb_total]``
-    with document columns in rank order, so diagonal targets are
-    ``rank_query_offset + arange(Nq_local)`` (:func:`score_contrastive_sharded`).
+    document shards are all-gathered.  They are ragged, so each is padded to a
+    common row count for the collective; the gathered buffer is never
+    compacted -- it is handed to the operator as one packed tensor in which
+    every rank's padding rows form one filler document whose score column is
+    dropped.  One forward launch therefore scores the rank's queries against
+    all documents.  Backward: one launch routes the gradient; the partial
+    ``grad_documents`` of the whole buffer is reduce-scattered so each owner
+    receives the sum for its shard; ``grad_queries`` stays local.  Scores come
+    back as ``[Nq_local, Nb_total]`` with document columns in rank order, so
+    diagonal targets are ``rank_query_offset + arange(Nq_local)``
+    (:func:`score_contrastive_sharded`).
 
 Both drivers take the operator namespace as a parameter so that their
 sharding / reassembly logic can be exercised on CPU ``gloo`` ranks with a
@@ -97,27 +99,66 @@ def score_candidates_padded_sharded(queries, documents, query_lengths, doc_lengt
 # ---------------------------------------------------------------------------
 
 def _gather_shards(documents: torch.Tensor, lengths: torch.Tensor, group, world: int):
-    """All-gather ragged packed shards.  Returns (per-rank token buffers, per-
-    rank int32 length vectors, async handle of the big gather or None)."""
+    """All-gather ragged packed shards into one buffer.
+
+    Every shard is padded to ``t_pad = longest shard + 1`` token rows, so the
+    gathered buffer ``[world * t_pad, D]`` holds rank r's tokens at rows
+    ``[r * t_pad, r * t_pad + T_r)`` followed by at least one padding row.  The
+    buffer is then described to the operators as ONE packed document tensor:
+    rank r's real documents followed by one filler document that covers its
+    padding rows.  Returns the buffer, the combined int32 offsets, the column
+    indices of the real (non-filler) documents, the number of columns, the
+    per-rank ``(tokens, documents)`` sizes and ``t_pad``."""
     dev = documents.device
     meta = torch.tensor([documents.shape[0], lengths.numel()], dtype=torch.int64, device=dev)
     metas = [torch.zeros_like(meta) for _ in range(world)]
     dist.all_gather(metas, meta, group=group)
     sizes = [(int(m[0].item()), int(m[1].item())) for m in metas]
-    t_max = max(s[0] for s in sizes)
+    t_pad = max(s[0] for s in sizes) + 1
     n_max = max(s[1] for s in sizes)
+
+    doc_pad = documents.new_zeros((t_pad, documents.shape[1]))
+    doc_pad[: documents.shape[0]] = documents
+    doc_parts = torch.empty((world * t_pad, documents.shape[1]), dtype=documents.dtype, device=dev)
+    if dist.get_backend(group) == "nccl":
+        handle = dist.all_gather_into_tensor(doc_parts, doc_pad, group=group, async_op=True)
+    else:
+        handle = dist.all_gather(list(doc_parts.view(world, t_pad, -1).unbind(0)), doc_pad,
+                                 group=group, async_op=True)
 
     len_pad = torch.zeros(n_max, dtype=torch.int32, device=dev)
     len_pad[: lengths.numel()] = lengths.to(torch.int32)
     len_parts = [torch.empty_like(len_pad) for _ in range(world)]
     dist.all_gather(len_parts, len_pad, group=group)
 
-    doc_pad = documents.new_zeros((t_max, documents.shape[1]))
-    doc_pad[: documents.shape[0]] = documents
-    doc_parts = [torch.empty_like(doc_pad) for _ in range(world)]
-    handle = dist.all_gather(doc_parts, doc_pad, group=group, async_op=True)
-    shards = [(doc_parts[r], len_parts[r][: sizes[r][1]], sizes[r][0]) for r in range(world)]
-    return shards, handle
+    # combined document list: real documents of rank r, then its filler.  The
+    # column indices of the real documents are built on the host (the sizes are
+    # already there), so selecting them later needs no device synchronisation.
+    fillers = torch.tensor([t_pad - s[0] for s in sizes], dtype=torch.int32).to(dev, non_blocking=True)
+    pieces, real_cols, base = [], [], 0
+    for r in range(world):
+        n_r = sizes[r][1]
+        pieces.append(len_parts[r][:n_r])
+        pieces.append(fillers[r:r + 1])
+        real_cols.extend(range(base, base + n_r))
+        base += n_r + 1
+    offsets = offsets_from_lengths(torch.cat(pieces))
+    real = torch.tensor(real_cols, dtype=torch.int64).to(dev, non_blocking=True)
+    handle.wait()
+    return doc_parts, offsets, real, base, sizes, t_pad
+
+
+def _reduce_scatter_rows(full: torch.Tensor, world: int, rank: int, group) -> torch.Tensor:
+    """Sum ``full [world * t_pad, D]`` over the ranks and return this rank's
+    ``[t_pad, D]`` block.  NCCL does it in one reduce-scatter; backends without
+    one (gloo, used by the CPU tests) all-reduce and slice."""
+    t_pad = full.shape[0] // world
+    if dist.get_backend(group) == "nccl":
+        out = torch.empty((t_pad, full.shape[1]), dtype=full.dtype, device=full.device)
+        dist.reduce_scatter_tensor(out, full, group=group)
+        return out
+    dist.all_reduce(full, group=group)
+    return full[rank * t_pad:(rank + 1) * t_pad]
 
 
 class _ShardedContrastive(torch.autograd.Function):
@@ -128,59 +169,32 @@ class _ShardedContrastive(torch.autograd.Function):
         d_local = documents.contiguous()
         lens_local = doc_lengths.to(torch.int32).contiguous()
         if world == 1:
-            shards = [(d_local, lens_local, d_local.shape[0])]
-            handle = None
+            docs_all, offsets, real, n_cols = d_local, offsets_from_lengths(lens_local), None, 0
+            t_pad = d_local.shape[0]
         else:
-            shards, handle = _gather_shards(d_local, lens_local, group, world)
-
-        order = [rank] + [r for r in range(world) if r != rank]  # own shard first
-        cols: List[Optional[torch.Tensor]] = [None] * world
-        saved = []
-        for step, r in enumerate(order):
-            if step == 1 and handle is not None:
-                handle.wait()  # remote shards are needed from here on
-            if r == rank:
-                d_r, lens_r, t_r = d_local, lens_local, d_local.shape[0]
-            else:
-                buf, lens_r, t_r = shards[r]
-                d_r = buf[:t_r]
-            off_r = offsets_from_lengths(lens_r)
-            s_r, a_r = ops.maxsim_contrastive_forward_with_argmax(q, d_r, off_r)
-            cols[r] = s_r
-            saved.append((r, d_r, off_r, a_r))
-        ctx.saved_chunks = saved
-        ctx.q = q
-        ctx.group = group
-        ctx.ops = ops
-        ctx.rank, ctx.world = rank, world
-        ctx.col_sizes = [c.shape[1] for c in cols]
-        return torch.cat(cols, dim=1)
+            docs_all, offsets, real, n_cols, _sizes, t_pad = _gather_shards(d_local, lens_local,
+                                                                            group, world)
+        scores_all, argmax = ops.maxsim_contrastive_forward_with_argmax(q, docs_all, offsets)
+        ctx.save_for_backward(q, docs_all, offsets, argmax)
+        ctx.real, ctx.n_cols = real, n_cols
+        ctx.group, ctx.ops, ctx.rank, ctx.world = group, ops, rank, world
+        ctx.t_local, ctx.t_pad = d_local.shape[0], t_pad
+        return scores_all if real is None else scores_all.index_select(1, real)
 
     @staticmethod
     def backward(ctx, dscore):
+        q, docs_all, offsets, argmax = ctx.saved_tensors
         ops, group, rank, world = ctx.ops, ctx.group, ctx.rank, ctx.world
         g = dscore.contiguous().to(torch.float32)
-        starts = [0]
-        for n in ctx.col_sizes:
-            starts.append(starts[-1] + n)
-        by_rank = {r: (d_r, off_r, a_r) for r, d_r, off_r, a_r in ctx.saved_chunks}
-        dq_total = None
-        dd_local = None
-        pending = []
-        # Collectives must be issued in the same order on every rank: owner 0, 1, ...
-        for r in range(world):
-            d_r, off_r, a_r = by_rank[r]
-            g_r = g[:, starts[r]:starts[r + 1]].contiguous()
-            dq_r, dd_r = ops.maxsim_contrastive_backward(g_r, ctx.q, d_r, off_r, a_r)
-            dq_total = dq_r if dq_total is None else dq_total.add_(dq_r)
-            if world > 1:
-                pending.append(dist.reduce(dd_r, dst=dist.get_global_rank(group, r) if group else r,
-                                           group=group, async_op=True))
-            if r == rank:
-                dd_local = dd_r
-        for h in pending:
-            h.wait()
-        return dq_total, dd_local, None, None, None
+        if ctx.real is not None:  # filler documents receive no gradient
+            g_all = torch.zeros((g.shape[0], ctx.n_cols), dtype=torch.float32, device=g.device)
+            g_all.index_copy_(1, ctx.real, g)
+            g = g_all
+        dq, dd_all = ops.maxsim_contrastive_backward(g, q, docs_all, offsets, argmax)
+        if world == 1:
+            return dq, dd_all, None, None, None
+        mine = _reduce_scatter_rows(dd_all, world, rank, group)
+        return dq, mine[: ctx.t_local].contiguous(), None, None, None
 
 
 def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, ops=None):
