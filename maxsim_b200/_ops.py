@@ -16,7 +16,9 @@ library, is an error.
 from __future__ import annotations
 
 import ctypes
+import os
 import types
+from pathlib import Path
 from ctypes import c_char_p, c_int, c_int64, c_void_p
 from typing import Tuple
 
@@ -57,8 +59,9 @@ def load_library() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.LIB_PATH
-    if not _build.is_current():
+    override = os.environ.get("MAXSIM_B200_LIBRARY")  # an alternative build, for A/B comparisons
+    path = _build.LIB_PATH if not override else Path(override)
+    if not override and not _build.is_current():
         try:
             _build.build()
         except RuntimeError as exc:

@@ -14,11 +14,17 @@
 //     8 steps of 16) for both accumulators against each staged tile and
 //     commits to mbarriers; accumulators are double-buffered in TMEM (512
 //     columns) so the tensor pipe runs ahead of the epilogue;
-//   * eight epilogue warps read their row's 128 similarities per tile with
-//     tcgen05.ld and fold them into a running maximum and first-index argmax
-//     held in registers, cutting at document boundaries; when a document ends
-//     the 32 row maxima of a query are summed with a warp shuffle tree.
-//     No similarity value is ever written to shared or global memory.
+//   * eight epilogue warps read their row's similarities with tcgen05.ld, 64
+//     columns at a time (the next 64 in flight meanwhile), and fold them into a
+//     running maximum and first-index argmax held in registers, cutting at
+//     document boundaries; when a document ends the 32 row maxima of a query
+//     are summed with a warp shuffle tree.  No similarity value is ever written
+//     to shared or global memory.
+//   * the epilogue, not the tensor pipe, sets the pace (with the epilogue
+//     disabled the TMA/MMA pipeline alone runs at 0.92 of the measured bf16
+//     peak), so its arithmetic is arranged for few instructions and much
+//     independent work: 3-input max trees, an argmax search that runs on the
+//     FMA pipe instead of compare/select pairs, two chunks folded per step.
 //
 // Every wait is bounded; a wait that runs out records a status bit and the
 // CTA drains to the common exit, where TMEM is released.
@@ -42,10 +48,10 @@ constexpr uint32_t kWaitLimit = 1u << 22;
 
 // A kernel configuration: MSUB accumulators of 128 rows per CTA (M = 128*MSUB)
 // and document tiles of BN tokens.  TMEM holds MSUB*BN*2 columns (<= 512).
-//   <2, 128>: M = 256,  8 epilogue warps, each folds 128 columns per tile
-//   <4,  64>: M = 512, 16 epilogue warps, each folds  64 columns per tile; four
-//             warps per scheduler hide the epilogue's dependent-issue latency
-//             and every staged document tile is used by twice as many queries.
+//   <2, 128>: M = 256,  8 epilogue warps, each folds 128 columns per tile (default)
+//   <4,  64>: M = 512, 16 epilogue warps, each folds  64 columns per tile; kept
+//             for comparison -- its shorter MMAs and single register buffer
+//             measured slower (TMA/MMA pipeline alone: 0.61 of peak).
 template <int MSUB, int BN>
 struct Cfg {
   static constexpr int kMSub = MSUB;
@@ -173,6 +179,81 @@ __device__ __forceinline__ int first_index_of_max(const float (&v)[32], float m)
   const float k = max32(key);
   if (!(k >= 8388608.0f)) return -1;
   return 31 - (__float_as_int(k) & 31);
+}
+
+// 64-column variants: one TMEM load and one fold per 64 similarities.  Twice
+// the independent work per dependent step (two max trees, two key sets), and
+// the per-chunk bookkeeping is paid once per 64 columns.
+__device__ __forceinline__ void tmem_ld64_issue(uint32_t taddr, uint32_t (&r)[64]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, "
+      "%32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, "
+      "%48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]),
+        "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]),
+        "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]),
+        "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]),
+        "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]),
+        "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]),
+        "=r"(r[62]), "=r"(r[63])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait64(uint32_t (&r)[64]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
+                 "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
+                 "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]),
+                 "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
+                 "+r"(r[30]), "+r"(r[31]), "+r"(r[32]), "+r"(r[33]), "+r"(r[34]), "+r"(r[35]),
+                 "+r"(r[36]), "+r"(r[37]), "+r"(r[38]), "+r"(r[39]), "+r"(r[40]), "+r"(r[41]),
+                 "+r"(r[42]), "+r"(r[43]), "+r"(r[44]), "+r"(r[45]), "+r"(r[46]), "+r"(r[47]),
+                 "+r"(r[48]), "+r"(r[49]), "+r"(r[50]), "+r"(r[51]), "+r"(r[52]), "+r"(r[53]),
+                 "+r"(r[54]), "+r"(r[55]), "+r"(r[56]), "+r"(r[57]), "+r"(r[58]), "+r"(r[59]),
+                 "+r"(r[60]), "+r"(r[61]), "+r"(r[62]), "+r"(r[63])
+               :
+               : "memory");
+}
+
+// Fold 64 similarities (two chunks of 32, a before b) of one document.
+template <bool ARGMAX>
+__device__ __forceinline__ void fold64(const float (&a)[32], const float (&b)[32], int base_ix,
+                                       float& run, int& idx) {
+  const float m = fmaxf(max32(a), max32(b));
+  if (ARGMAX) {
+    if (__any_sync(0xffffffffu, m > run)) {
+      const float kScale = 8.507059173023462e37f;  // 2^126
+      float ka[32], kb[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        ka[j] = fmaf(a[j] - m, kScale, 8388608.0f + (float)(63 - j));
+        kb[j] = fmaf(b[j] - m, kScale, 8388608.0f + (float)(31 - j));
+      }
+      const float k = fmaxf(max32(ka), max32(kb));
+      if (m > run) {
+        int first;
+        if (k >= 8388608.0f) {
+          first = 63 - (__float_as_int(k) & 63);
+        } else {  // infinite maximum: compare loop
+          first = 63;
+#pragma unroll
+          for (int j = 31; j >= 0; --j) first = (b[j] == m) ? 32 + j : first;
+#pragma unroll
+          for (int j = 31; j >= 0; --j) first = (a[j] == m) ? j : first;
+        }
+        run = m;
+        idx = base_ix + first;
+      }
+    }
+  } else {
+    run = fmaxf(run, m);
+  }
 }
 
 // Folds 32 similarities of one document into the row's running maximum and
@@ -355,67 +436,101 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr0 =
             tmem_base + ((uint32_t)(quad * 32) << 16) + acc * (kMSub * kBN) + sub * kBN;
-        // Chunks of 32 columns, the next chunk's TMEM load in flight while the
-        // current one is folded.
-        constexpr int kBufs = C::kPrefetch ? 2 : 1;
-        uint32_t raw[kBufs][32];
         const int tok_tile = s0 + tile * kBN;
-        int n_chunks = (min(s1 - tok_tile, kBN) + 31) >> 5;   // chunks that hold tokens of this item
-        if (d >= d_hi) n_chunks = 0;
-        if (C::kPrefetch && n_chunks > 0) tmem_ld32_issue(taddr0, raw[0]);
+        int n_valid = min(s1 - tok_tile, kBN);  // columns of this tile that hold tokens of the item
+        if (d >= d_hi) n_valid = 0;
+
+        // document d complete for this warp's query: sum the 32 row maxima, store
+        auto finish_document = [&]() {
+          float sum = run;
 #pragma unroll
-        for (int c4 = 0; c4 < kBN / 32; ++c4) {
-          if (c4 < n_chunks) {
-            constexpr int kNoBuf = 0;
-            const int cur = C::kPrefetch ? (c4 & 1) : kNoBuf;
-            if (!C::kPrefetch) tmem_ld32_issue(taddr0 + c4 * 32, raw[0]);
-            tmem_ld_wait(raw[cur]);
-            if (C::kPrefetch && c4 + 1 < n_chunks)
-              tmem_ld32_issue(taddr0 + (c4 + 1) * 32, raw[(c4 + 1) & (kBufs - 1)]);
-            float v[32];
+          for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+          if (q_ok) {
+            const int64_t pair = (int64_t)q * P.Nb + d;
+            if (ARGMAX) P.argmax[pair * kLq + lane] = idx;
+            if (lane == 0) P.scores[pair] = sum;
+          }
+          run = neg_inf();
+          idx = 0;
+          ++d;
+          dstart = dend;
+          if (d < d_hi) dend = __ldg(doff + d + 1);
+        };
+        // 32 columns starting at token tok0, cut at document boundaries
+        auto fold_chunk = [&](const float (&v)[32], int tok0) {
+          int col = 0;
+          while (col < 32 && d < d_hi) {
+            const int seg_end = min(32, dend - tok0);
+            const int base_ix = tok0 - dstart;
+            // Columns of this chunk that belong to document d: [col, seg_end).
+            if (col == 0 && seg_end == 32) {
+              fold32<ARGMAX>(v, base_ix, run, idx);
+            } else if (ARGMAX) {
+              // boundary chunk: per-column predicated update (fewest instructions)
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[cur][j]);
-            const int tok0 = tok_tile + c4 * 32;
-            int col = 0;
-            while (col < 32 && d < d_hi) {
-              const int seg_end = min(32, dend - tok0);
-              const int base_ix = tok0 - dstart;
-              // Columns of this chunk that belong to document d: [col, seg_end).
-              if (col == 0 && seg_end == 32) {
-                fold32<ARGMAX>(v, base_ix, run, idx);
-              } else if (ARGMAX) {
-                // boundary chunk: per-column predicated update (fewest instructions)
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  if (j >= col && j < seg_end) {
-                    if (v[j] > run) { run = v[j]; idx = base_ix + j; }
-                  }
+              for (int j = 0; j < 32; ++j) {
+                if (j >= col && j < seg_end) {
+                  if (v[j] > run) { run = v[j]; idx = base_ix + j; }
                 }
+              }
+            } else {
+              float w[32];
+              const unsigned span = (unsigned)(seg_end - col);
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                w[j] = ((unsigned)(j - col) < span) ? v[j] : neg_inf();
+              fold32<false>(w, base_ix, run, idx);
+            }
+            col = max(col, seg_end);
+            if (tok0 + col >= dend) finish_document();
+          }
+        };
+
+        if constexpr (C::kPrefetch && (kBN % 64 == 0)) {
+          // 64 columns per step; the next 64 are in flight while these are folded.
+          uint32_t raw[2][64];
+          if (n_valid > 0) tmem_ld64_issue(taddr0, raw[0]);
+#pragma unroll
+          for (int h = 0; h < kBN / 64; ++h) {
+            if (h * 64 < n_valid) {
+              tmem_ld_wait64(raw[h & 1]);
+              if (h + 1 < kBN / 64 && (h + 1) * 64 < n_valid)
+                tmem_ld64_issue(taddr0 + (h + 1) * 64, raw[(h + 1) & 1]);
+              float va[32], vb[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                va[j] = __uint_as_float(raw[h & 1][j]);
+                vb[j] = __uint_as_float(raw[h & 1][32 + j]);
+              }
+              const int tok0 = tok_tile + h * 64;
+              if (d < d_hi && tok0 + 64 <= dend) {
+                fold64<ARGMAX>(va, vb, tok0 - dstart, run, idx);
+                if (tok0 + 64 == dend) finish_document();
               } else {
-                float w[32];
-                const unsigned span = (unsigned)(seg_end - col);
-#pragma unroll
-                for (int j = 0; j < 32; ++j)
-                  w[j] = ((unsigned)(j - col) < span) ? v[j] : neg_inf();
-                fold32<false>(w, base_ix, run, idx);
+                fold_chunk(va, tok0);
+                if (h * 64 + 32 < n_valid) fold_chunk(vb, tok0 + 32);
               }
-              col = max(col, seg_end);
-              if (tok0 + col >= dend) {
-                // document d complete for this warp's query
-                float sum = run;
+            }
+          }
+        } else {
+          // 32 columns per step
+          constexpr int kBufs = C::kPrefetch ? 2 : 1;
+          uint32_t raw[kBufs][32];
+          const int n_chunks = (n_valid + 31) >> 5;
+          if (C::kPrefetch && n_chunks > 0) tmem_ld32_issue(taddr0, raw[0]);
 #pragma unroll
-                for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-                if (q_ok) {
-                  const int64_t pair = (int64_t)q * P.Nb + d;
-                  if (ARGMAX) P.argmax[pair * kLq + lane] = idx;
-                  if (lane == 0) P.scores[pair] = sum;
-                }
-                run = neg_inf();
-                idx = 0;
-                ++d;
-                dstart = dend;
-                if (d < d_hi) dend = __ldg(doff + d + 1);
-              }
+          for (int c4 = 0; c4 < kBN / 32; ++c4) {
+            if (c4 < n_chunks) {
+              constexpr int kNoBuf = 0;
+              const int cur = C::kPrefetch ? (c4 & 1) : kNoBuf;
+              if (!C::kPrefetch) tmem_ld32_issue(taddr0 + c4 * 32, raw[0]);
+              tmem_ld_wait(raw[cur]);
+              if (C::kPrefetch && c4 + 1 < n_chunks)
+                tmem_ld32_issue(taddr0 + (c4 + 1) * 32, raw[(c4 + 1) & (kBufs - 1)]);
+              float v[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[cur][j]);
+              fold_chunk(v, tok_tile + c4 * 32);
             }
           }
         }

@@ -56,7 +56,7 @@ SHAPES = [
 
 @pytest.mark.parametrize("Nq,d_lens", SHAPES)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("path", [3, 4])  # 3: configuration chosen by Nq, 4: M = 256 forced
+@pytest.mark.parametrize("path", [3, 5])  # 3: M = 256 (default), 5: M = 512 with 64-token tiles
 def test_tc05_matches_oracle(Nq, d_lens, dtype, path):
     _ops.set_forward_path(path)
     q, d, off = _make(Nq, d_lens, dtype, 11)
