@@ -71,63 +71,79 @@ def _peaks():
 # ---------------------------------------------------------------------------
 
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap,utilization.gpu")
+    """Samples SM clock and clock-event (throttle) reasons of one GPU while the
+    benchmark runs.  Uses NVML from a thread of this process: two light queries
+    per sample.  (An `nvidia-smi -lms` subprocess polling many fields was seen
+    to stall kernels of the timed loop for 10-20 ms at a time.)"""
 
-    def __init__(self, device_index: int):
-        self.proc = None
-        self.path = None
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap"}
+
+    def __init__(self, device_index: int, interval_s: float = 0.05):
+        self.interval = interval_s
+        self.samples = []
+        self._stop = None
+        self._thread = None
+        self._handle = None
+        self._nvml = None
         try:
+            import pynvml
+            pynvml.nvmlInit()
             uuid = str(torch.cuda.get_device_properties(device_index).uuid)
             ident = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
-        except Exception:
-            ident = str(device_index)
-        self.ident = ident
-
-    def start(self):
-        try:
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.ident}", f"--query-gpu={self.FIELDS}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except Exception:
-            self.proc = None
-
-    def stop(self):
-        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
-        if self.proc is None:
-            return out
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        rows = []
-        try:
-            for line in open(self.path):
-                parts = [x.strip() for x in line.split(",")]
-                if len(parts) >= 7 and parts[0].isdigit():
-                    rows.append(parts)
-        except Exception:
-            pass
-        finally:
             try:
-                os.unlink(self.path)
+                self._handle = pynvml.nvmlDeviceGetHandleByUUID(ident.encode())
+            except Exception:
+                self._handle = pynvml.nvmlDeviceGetHandleByUUID(ident)
+            self._nvml = pynvml
+        except Exception:
+            self._handle = None
+
+    def _loop(self):
+        nv, h = self._nvml, self._handle
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                try:
+                    reasons = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                except Exception:
+                    reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((mhz, int(reasons)))
             except Exception:
                 pass
+            self._stop.wait(self.interval)
+
+    def start(self):
+        if self._handle is None:
+            return
+        import threading
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+        self._thread.start()
+
+    def mark(self):
+        """Index of the next sample: brackets a region of interest."""
+        return len(self.samples)
+
+    def stop(self, begin: int = 0, end=None):
+        out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+        if self._thread is None:
+            return out
+        self._stop.set()
+        self._thread.join(timeout=2)
+        rows = self.samples[begin:end] or self.samples
         if not rows:
             return out
-        busy = [r for r in rows if r[6].isdigit() and int(r[6]) >= 50] or rows
-        out["sm_mhz"] = statistics.median(int(r[0]) for r in busy)
-        out["sm_max_mhz"] = max(int(r[1]) for r in rows)
-        out["samples"] = len(busy)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for i, n in enumerate(names):
-            if any(r[2 + i].lower().startswith("active") for r in busy):
-                out["reasons"].append(n)
+        try:
+            out["sm_max_mhz"] = self._nvml.nvmlDeviceGetMaxClockInfo(self._handle, self._nvml.NVML_CLOCK_SM)
+        except Exception:
+            out["sm_max_mhz"] = max(r[0] for r in rows)
+        out["sm_mhz"] = statistics.median(r[0] for r in rows)
+        out["samples"] = len(rows)
+        seen = 0
+        for _, r in rows:
+            seen |= r
+        out["reasons"] = [name for bit, name in self.REASONS.items() if seen & bit]
         return out
 
 
@@ -440,11 +456,13 @@ def run_gpu_arm(args):
 
     sampler = ClockSampler(local_rank)
     sampler.start()
+    load_begin = 0
 
     def step():
         return _ops.ops.maxsim_padded_forward(q_flat, qlen, d_flat, dlen_flat, Lq, Ld, C)
 
     # --- device-resident throughput -----------------------------------------
+    load_begin = sampler.mark()
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
@@ -467,7 +485,7 @@ def run_gpu_arm(args):
     kernel_ms = statistics.mean(launch_ms)
 
     if args.kernel_only:
-        sampler.stop()
+        sampler.stop(load_begin)
         if rank == 0:
             print(json.dumps({"profile_run": True, "workload": WORKLOAD, "pairs": pairs,
                               "algorithmic_bytes": algo_bytes, "kernel_ms": kernel_ms,
@@ -535,7 +553,9 @@ def run_gpu_arm(args):
         for _ in range(10):
             step()
         torch.cuda.synchronize()
-    clocks = sampler.stop()
+    clocks = sampler.stop(load_begin)
+    clocks["note"] = ("NVML samples every 50 ms from the start of warm-up through the timed steps, "
+                      "the end-to-end steps and a 1.5 s loop of the same kernel")
     status = _ops.device_status()
 
     # --- max over ranks ------------------------------------------------------
@@ -574,6 +594,8 @@ def run_gpu_arm(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"],
                          "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                          "peak_source": peaks["source"], "kernel_ms": kernel_ms,
+                         "kernel_ms_min_median_max": [min(launch_ms), statistics.median(launch_ms),
+                                                      max(launch_ms)],
                          "algorithmic_bytes": algo_bytes,
                          "traffic": (None if NCU_TRAFFIC_RATIO is None
                                      else NCU_TRAFFIC_RATIO * algo_bytes)},
