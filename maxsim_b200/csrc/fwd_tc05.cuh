@@ -14,17 +14,17 @@
 //     8 steps of 16) for both accumulators against each staged tile and
 //     commits to mbarriers; accumulators are double-buffered in TMEM (512
 //     columns) so the tensor pipe runs ahead of the epilogue;
-//   * eight epilogue warps read their row's similarities with tcgen05.ld, 64
-//     columns at a time (the next 64 in flight meanwhile), and fold them into a
-//     running maximum and first-index argmax held in registers, cutting at
-//     document boundaries; when a document ends the 32 row maxima of a query
-//     are summed with a warp shuffle tree.  No similarity value is ever written
-//     to shared or global memory.
+//   * eight epilogue warps read their row's 128 similarities of a tile into
+//     registers with tcgen05.ld and hand the TMEM stage back at once, then fold
+//     them into a running maximum and first-index argmax held in registers,
+//     cutting at document boundaries; when a document ends the 32 row maxima of
+//     a query are summed with a warp shuffle tree.  No similarity value is ever
+//     written to shared or global memory.
 //   * the epilogue, not the tensor pipe, sets the pace (with the epilogue
 //     disabled the TMA/MMA pipeline alone runs at 0.92 of the measured bf16
 //     peak), so its arithmetic is arranged for few instructions and much
 //     independent work: 3-input max trees, an argmax search that runs on the
-//     FMA pipe instead of compare/select pairs, two chunks folded per step.
+//     FMA pipe instead of compare/select pairs, a whole tile folded per step.
 //
 // Every wait is bounded; a wait that runs out records a status bit and the
 // CTA drains to the common exit, where TMEM is released.
@@ -181,9 +181,7 @@ __device__ __forceinline__ int first_index_of_max(const float (&v)[32], float m)
   return 31 - (__float_as_int(k) & 31);
 }
 
-// 64-column variants: one TMEM load and one fold per 64 similarities.  Twice
-// the independent work per dependent step (two max trees, two key sets), and
-// the per-chunk bookkeeping is paid once per 64 columns.
+// 64-column TMEM load (two of them bring a whole 128-token tile to registers).
 __device__ __forceinline__ void tmem_ld64_issue(uint32_t taddr, uint32_t (&r)[64]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
@@ -242,6 +240,65 @@ __device__ __forceinline__ void fold64(const float (&a)[32], const float (&b)[32
           first = 63 - (__float_as_int(k) & 63);
         } else {  // infinite maximum: compare loop
           first = 63;
+#pragma unroll
+          for (int j = 31; j >= 0; --j) first = (b[j] == m) ? 32 + j : first;
+#pragma unroll
+          for (int j = 31; j >= 0; --j) first = (a[j] == m) ? j : first;
+        }
+        run = m;
+        idx = base_ix + first;
+      }
+    }
+  } else {
+    run = fmaxf(run, m);
+  }
+}
+
+// Fold a whole 128-column tile of one document (four chunks a, b, c, d in order).
+template <bool ARGMAX>
+__device__ __forceinline__ void fold128(const float (&a)[32], const float (&b)[32],
+                                        const float (&c)[32], const float (&d)[32], int base_ix,
+                                        float& run, int& idx) {
+  const float m = fmaxf(fmaxf(max32(a), max32(b)), fmaxf(max32(c), max32(d)));
+  if (ARGMAX) {
+    if (__any_sync(0xffffffffu, m > run)) {
+      const float kScale = 8.507059173023462e37f;  // 2^126
+      float k4[4];
+      {
+        float t[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) t[j] = fmaf(a[j] - m, kScale, 8388608.0f + (float)(127 - j));
+        k4[0] = max32(t);
+      }
+      {
+        float t[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) t[j] = fmaf(b[j] - m, kScale, 8388608.0f + (float)(95 - j));
+        k4[1] = max32(t);
+      }
+      {
+        float t[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) t[j] = fmaf(c[j] - m, kScale, 8388608.0f + (float)(63 - j));
+        k4[2] = max32(t);
+      }
+      {
+        float t[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) t[j] = fmaf(d[j] - m, kScale, 8388608.0f + (float)(31 - j));
+        k4[3] = max32(t);
+      }
+      const float k = fmaxf(fmaxf(k4[0], k4[1]), fmaxf(k4[2], k4[3]));
+      if (m > run) {
+        int first;
+        if (k >= 8388608.0f) {
+          first = 127 - (__float_as_int(k) & 127);
+        } else {  // infinite maximum: compare loop
+          first = 127;
+#pragma unroll
+          for (int j = 31; j >= 0; --j) first = (d[j] == m) ? 96 + j : first;
+#pragma unroll
+          for (int j = 31; j >= 0; --j) first = (c[j] == m) ? 64 + j : first;
 #pragma unroll
           for (int j = 31; j >= 0; --j) first = (b[j] == m) ? 32 + j : first;
 #pragma unroll
@@ -486,32 +543,52 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         };
 
-        if constexpr (C::kPrefetch && (kBN % 64 == 0)) {
-          // 64 columns per step; the next 64 are in flight while these are folded.
+        if constexpr (kBN == 128 && C::kPrefetch) {
+          // The whole tile goes to registers at once and the TMEM stage is handed
+          // back before any arithmetic, so the tensor pipe never waits on the fold.
           uint32_t raw[2][64];
-          if (n_valid > 0) tmem_ld64_issue(taddr0, raw[0]);
+          if (n_valid > 0) {
+            tmem_ld64_issue(taddr0, raw[0]);
+            if (n_valid > 64) tmem_ld64_issue(taddr0 + 64, raw[1]);
+            tmem_ld_wait64(raw[0]);
+            tmem_ld_wait64(raw[1]);
+          }
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          __syncwarp();
+          if (lane == 0) mbar_arrive(t_empty + 8 * acc);
+          if (n_valid > 0) {
+            float va[32], vb[32], vc[32], vd[32];
 #pragma unroll
-          for (int h = 0; h < kBN / 64; ++h) {
-            if (h * 64 < n_valid) {
-              tmem_ld_wait64(raw[h & 1]);
-              if (h + 1 < kBN / 64 && (h + 1) * 64 < n_valid)
-                tmem_ld64_issue(taddr0 + (h + 1) * 64, raw[(h + 1) & 1]);
-              float va[32], vb[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                va[j] = __uint_as_float(raw[h & 1][j]);
-                vb[j] = __uint_as_float(raw[h & 1][32 + j]);
-              }
-              const int tok0 = tok_tile + h * 64;
-              if (d < d_hi && tok0 + 64 <= dend) {
-                fold64<ARGMAX>(va, vb, tok0 - dstart, run, idx);
-                if (tok0 + 64 == dend) finish_document();
+            for (int j = 0; j < 32; ++j) {
+              va[j] = __uint_as_float(raw[0][j]);
+              vb[j] = __uint_as_float(raw[0][32 + j]);
+              vc[j] = __uint_as_float(raw[1][j]);
+              vd[j] = __uint_as_float(raw[1][32 + j]);
+            }
+            if (d < d_hi && tok_tile + 128 <= dend) {
+              fold128<ARGMAX>(va, vb, vc, vd, tok_tile - dstart, run, idx);
+              if (tok_tile + 128 == dend) finish_document();
+            } else {
+              if (d < d_hi && tok_tile + 64 <= dend) {
+                fold64<ARGMAX>(va, vb, tok_tile - dstart, run, idx);
+                if (tok_tile + 64 == dend) finish_document();
               } else {
-                fold_chunk(va, tok0);
-                if (h * 64 + 32 < n_valid) fold_chunk(vb, tok0 + 32);
+                fold_chunk(va, tok_tile);
+                if (32 < n_valid) fold_chunk(vb, tok_tile + 32);
+              }
+              if (64 < n_valid) {
+                if (d < d_hi && tok_tile + 128 <= dend) {
+                  fold64<ARGMAX>(vc, vd, tok_tile + 64 - dstart, run, idx);
+                  if (tok_tile + 128 == dend) finish_document();
+                } else {
+                  fold_chunk(vc, tok_tile + 64);
+                  if (96 < n_valid) fold_chunk(vd, tok_tile + 96);
+                }
               }
             }
           }
+          if (++acc == kAccStages) { acc = 0; aph ^= 1u; }
+          continue;
         } else {
           // 32 columns per step
           constexpr int kBufs = C::kPrefetch ? 2 : 1;
