@@ -85,6 +85,17 @@ MAXSIM_API int maxsim_b200_layout_stats(const void* offsets, int64_t n_offsets,
                                         const void* ids, int64_t n_ids,
                                         int index_bytes, int64_t* out8, void* stream);
 
+/* Fused in-batch contrastive loss over a score matrix (no reference
+ * counterpart; callers of the reference build it from softmax / nll kernels,
+ * tests/test_train_convergence.py:34-45).  scores [Nq, Nb] float, targets [Nq]
+ * int64 column of each query's positive.  Writes loss_rows [Nq] =
+ * logsumexp(scores[q]/T) - scores[q, target]/T and, when dscore is not NULL,
+ * dscore [Nq, Nb] = (softmax(scores[q]/T) - onehot(target)) * grad_scale / T. */
+MAXSIM_API int maxsim_b200_contrastive_ce(const float* scores, const int64_t* targets,
+                                          float* loss_rows, float* dscore,
+                                          int64_t Nq, int64_t Nb, float temperature,
+                                          float grad_scale, void* stream);
+
 /* ------------------------------------------------------------------------
  * Packed pair grids.
  * queries [total_q_tokens, dim], query_offsets [n_queries+1],

@@ -35,7 +35,7 @@ __all__ = [
     "score_contrastive", "score_contrastive_with_argmax", "score_contrastive_train",
     "score_padded", "score_padded_with_argmax", "score_padded_train",
     "score_packed", "score_packed_with_argmax", "score_packed_train",
-    "lengths_from_prefix_mask",
+    "lengths_from_prefix_mask", "contrastive_loss",
 ]
 
 __version__ = "0.1.0"
@@ -256,6 +256,55 @@ score_padded_train = score_candidates_padded_train
 score_packed = score_pairs_packed
 score_packed_with_argmax = score_pairs_packed_with_argmax
 score_packed_train = score_pairs_packed_train
+
+
+class _ContrastiveLossFn(torch.autograd.Function):
+    """Forward: scores + argmax, then one kernel that produces the mean
+    cross-entropy and the gradient with respect to the scores.  Backward: the
+    saved score gradient, scaled by the upstream scalar, goes straight into the
+    routing kernels -- no softmax / nll kernels and no [Nq, Nb] autograd graph."""
+
+    @staticmethod
+    def forward(ctx, queries, documents, document_offsets, targets, temperature):
+        from . import _ops
+        q = queries.contiguous()
+        d = documents.contiguous()
+        off = document_offsets.to(dtype=torch.int32).contiguous()
+        scores, argmax = ops.maxsim_contrastive_forward_with_argmax(q, d, off)
+        loss_rows, dscore = _ops.contrastive_ce(scores, targets, temperature,
+                                                1.0 / max(1, scores.shape[0]), True)
+        ctx.save_for_backward(q, d, off, argmax, dscore)
+        return loss_rows.mean()
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        q, d, off, argmax, dscore = ctx.saved_tensors
+        g = dscore * grad_out.to(torch.float32)
+        dq, dd = ops.maxsim_contrastive_backward(g, q, d, off, argmax)
+        return dq, dd, None, None, None
+
+
+@_eager
+def contrastive_loss(queries, documents, document_offsets, targets=None, *,
+                     temperature: float = 1.0) -> torch.Tensor:
+    """Mean in-batch cross-entropy of the contrastive score matrix, fused with
+    the scoring operator (an extension; the reference has no such function).
+
+    Equivalent to ``cross_entropy(score_contrastive_train(q, d, off) /
+    temperature, targets)`` with ``targets`` defaulting to ``arange(Nq)``
+    (query i's positive is document i); differentiable with respect to
+    ``queries`` and ``documents``."""
+    _v.check_contrastive(queries, documents, document_offsets)
+    if not temperature > 0:
+        raise ValueError(f"temperature must be > 0; got {temperature}")
+    Nq, Nb = queries.shape[0], document_offsets.numel() - 1
+    if targets is None:
+        if Nq > Nb:
+            raise ValueError(f"default diagonal targets need Nq <= Nb; got Nq={Nq}, Nb={Nb}")
+        targets = torch.arange(Nq, device=queries.device)
+    elif tuple(targets.shape) != (Nq,):
+        raise ValueError(f"targets must have shape [Nq={Nq}]; got {tuple(targets.shape)}")
+    return _ContrastiveLossFn.apply(queries, documents, document_offsets, targets, float(temperature))
 
 
 def lengths_from_prefix_mask(mask: torch.Tensor) -> torch.Tensor:

@@ -40,6 +40,7 @@ _SIGNATURES = {
     "maxsim_b200_launch_count": (c_int64, []),
     "maxsim_b200_set_forward_path": (None, [c_int]),
     "maxsim_b200_layout_stats": (c_int, [_P, _I64, _P, _I64, c_int, _P, _P]),
+    "maxsim_b200_contrastive_ce": (c_int, [_P] * 4 + [_I64] * 2 + [ctypes.c_float] * 2 + [_P]),
     "maxsim_forward": (c_int, [_P] * 7 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_forward_with_argmax": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_backward": (c_int, [_P] * 10 + [_I64] * 7 + [c_int, _P]),
@@ -121,6 +122,25 @@ def layout_stats(items) -> list:
                 ref.element_size(), out[row].data_ptr(), _stream_ptr())
             _check(rc, "maxsim_b200_layout_stats")
     return out.tolist()
+
+
+def contrastive_ce(scores: torch.Tensor, targets: torch.Tensor, temperature: float,
+                   grad_scale: float, want_grad: bool):
+    """Row-wise cross-entropy of ``scores [Nq, Nb]`` (fp32, CUDA) against
+    ``targets [Nq]``; returns ``(loss_rows [Nq], dscore [Nq, Nb] or None)``."""
+    dev = _require_cuda(scores, targets)
+    s = scores.contiguous().to(torch.float32)
+    t = targets.contiguous().to(torch.int64)
+    if s.dim() != 2 or t.dim() != 1 or t.shape[0] != s.shape[0]:
+        raise RuntimeError("scores must be [Nq, Nb] and targets [Nq]")
+    loss_rows = torch.empty((s.shape[0],), dtype=torch.float32, device=dev)
+    dscore = torch.empty_like(s) if want_grad else None
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_b200_contrastive_ce(
+            _ptr(s), _ptr(t), _ptr(loss_rows), _ptr(dscore) if dscore is not None else 0,
+            s.shape[0], s.shape[1], float(temperature), float(grad_scale), _stream_ptr())
+    _check(rc, "maxsim_b200_contrastive_ce")
+    return loss_rows, dscore
 
 
 def _stream_ptr() -> int:

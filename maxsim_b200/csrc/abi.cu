@@ -13,6 +13,7 @@
 #include "fwd_simt.cuh"
 #include "fwd_tc05.cuh"
 #include "layout_stats.cuh"
+#include "loss.cuh"
 
 namespace maxsim {
 
@@ -46,16 +47,32 @@ int launch_check(const char* what) {
   return MAXSIM_OK;
 }
 
+// Per-device caches below are written with the same value by every thread that
+// races on them, through atomics, so concurrent first calls are harmless.
+constexpr int kMaxDevices = 64;
+
 int sm_count() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[kMaxDevices];
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
+}
+
+// Opt a kernel in to `smem` bytes of dynamic shared memory, once per device.
+template <typename Kernel>
+int ensure_smem(Kernel kern, size_t smem, std::atomic<unsigned char>* done) {
+  int dev = 0;
+  MAXSIM_CUDA(cudaGetDevice(&dev));
+  const bool track = dev >= 0 && dev < kMaxDevices;
+  if (track && done[dev].load(std::memory_order_acquire)) return MAXSIM_OK;
+  MAXSIM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (track) done[dev].store(1, std::memory_order_release);
+  return MAXSIM_OK;
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -84,13 +101,8 @@ template <typename T, int DIM, int LAYOUT, bool ARGMAX>
 int launch_mma_dim(const PairTable& t, float* scores, int32_t* argmax, cudaStream_t st) {
   auto kern = fwd_mma_kernel<T, DIM, LAYOUT, ARGMAX>;
   constexpr size_t smem = mma_smem_bytes<DIM>();
-  static bool configured[64] = {false};
-  int dev = 0;
-  MAXSIM_CUDA(cudaGetDevice(&dev));
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    MAXSIM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    if (dev >= 0 && dev < 64) configured[dev] = true;
-  }
+  static std::atomic<unsigned char> configured[kMaxDevices];
+  if (int rc = ensure_smem(kern, smem, configured)) return rc;
   const int sms = sm_count();
   const int64_t warps_full = (int64_t)sms * kMmaWarps;
   int ppc = (int)(t.n_pairs / (warps_full * 4));
@@ -211,13 +223,8 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
           Nb < (1ll << 31) && Nq * (int64_t)t.q_slots < (1ll << 31)) {
         auto kern = bwd_dd_invert_kernel<T>;
         constexpr size_t smem = inv_smem_bytes();
-        static bool configured[64] = {false};
-        int dev = 0;
-        MAXSIM_CUDA(cudaGetDevice(&dev));
-        if (dev < 0 || dev >= 64 || !configured[dev]) {
-          MAXSIM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-          if (dev >= 0 && dev < 64) configured[dev] = true;
-        }
+        static std::atomic<unsigned char> configured[kMaxDevices];
+        if (int rc = ensure_smem(kern, smem, configured)) return rc;
         // One CTA per document.  Documents longer than kInvBins tokens are
         // covered by the kernel's stride over token chunks; a second CTA row
         // helps only when the mean document is that long.
@@ -322,6 +329,19 @@ int maxsim_b200_layout_stats(const void* offsets, int64_t n_offsets, const void*
   else
     return fail(MAXSIM_EINVAL, "index_bytes must be 4 or 8");
   return launch_check("layout_stats_kernel");
+}
+
+int maxsim_b200_contrastive_ce(const float* scores, const int64_t* targets, float* loss_rows,
+                               float* dscore, int64_t Nq, int64_t Nb, float temperature,
+                               float grad_scale, void* stream) {
+  if (Nq < 0 || Nb <= 0 || Nb >= (1ll << 31) || Nq >= (1ll << 31))
+    return fail(MAXSIM_EINVAL, "score matrix sizes must be positive and fit int32");
+  if (!(temperature > 0.f)) return fail(MAXSIM_EINVAL, "temperature must be > 0");
+  if (Nq == 0) return MAXSIM_OK;
+  if (!scores || !targets || !loss_rows) return fail(MAXSIM_EINVAL, "null pointer argument");
+  contrastive_ce_kernel<<<(unsigned)Nq, kLossThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      scores, targets, loss_rows, dscore, (int)Nb, 1.0f / temperature, grad_scale);
+  return launch_check("contrastive_ce_kernel");
 }
 
 int maxsim_forward(const void* queries, const int32_t* query_offsets, const void* documents,

@@ -8,8 +8,9 @@
 //     row has one owner warp that walks its candidates / documents and sums
 //     in registers -- no atomics, one store per element, deterministic;
 //   * grad_d of the padded layout has one owner warp per document slab;
-//   * grad_d of the contrastive layout accumulates per document segment in
-//     shared memory (one CTA per document chunk) and stores once;
+//   * grad_d of the contrastive layout inverts the argmax per document in
+//     shared memory (counting sort of the entries by winning token) and then
+//     gathers, one owner warp per document token, one store per row;
 //   * packed pair grids, whose pair list is arbitrary, use vector reductions
 //     (red.global.add) after a zero fill.
 #pragma once

@@ -32,6 +32,8 @@
 
 #include <cuda.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "fwd_mma.cuh"
 
@@ -639,17 +641,16 @@ typedef CUresult (*TensorMapEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint3
                                       CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 inline TensorMapEncodeFn tensor_map_encoder() {
-  static TensorMapEncodeFn fn = nullptr;
-  static bool tried = false;
-  if (!tried) {
-    tried = true;
+  // function-local static: initialised once, thread-safe since C++11
+  static const TensorMapEncodeFn fn = []() -> TensorMapEncodeFn {
     void* p = nullptr;
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) ==
             cudaSuccess &&
         qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<TensorMapEncodeFn>(p);
-  }
+      return reinterpret_cast<TensorMapEncodeFn>(p);
+    return nullptr;
+  }();
   return fn;
 }
 
@@ -711,14 +712,15 @@ int launch_tc05_cfg(const PairTable& t, float* scores, int32_t* argmax, int dtyp
             ((uint32_t)(tc05::kBM >> 4) << 24);
 
   auto kern = tc05::fwd_tc05_kernel<ARGMAX, MSUB, BN>;
-  static bool configured[64] = {false};
+  static std::atomic<unsigned char> configured[64];  // same value from every racing thread
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -3;
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
+  const bool track = dev >= 0 && dev < 64;
+  if (!track || !configured[dev].load(std::memory_order_acquire)) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              (int)C::kSmemBytes) != cudaSuccess)
       return -3;
-    if (dev >= 0 && dev < 64) configured[dev] = true;
+    if (track) configured[dev].store(1, std::memory_order_release);
   }
   const int grid = (int)(n_items < sms ? n_items : sms);
   kern<<<grid, C::kThreads, C::kSmemBytes, st>>>(tm_q, tm_d, P);

@@ -186,3 +186,41 @@ def test_training_reduces_contrastive_loss():
         opt.step()
         losses.append(float(loss))
     assert losses[-1] < 0.7 * losses[0], losses[::10]
+
+
+@pytest.mark.parametrize("temperature", [1.0, 0.05])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_fused_contrastive_loss_matches_cross_entropy(temperature, dtype):
+    """contrastive_loss == cross_entropy(score_contrastive_train / T, targets),
+    values and gradients (the unfused expression is the one the reference's
+    callers write, tests/test_train_convergence.py:34-45)."""
+    g = torch.Generator().manual_seed(7)
+    Nq, d_lens, dim = 24, [40, 7, 130, 64, 65] * 6, 128
+    qn = torch.nn.functional.normalize(torch.randn(Nq, 32, dim, generator=g), dim=-1)
+    dn = torch.nn.functional.normalize(torch.randn(sum(d_lens), dim, generator=g), dim=-1)
+    off = torch.tensor(np.concatenate([[0], np.cumsum(d_lens)]), dtype=torch.int32, device=DEV)
+    targets = torch.randint(0, len(d_lens), (Nq,), generator=g).to(DEV)
+    q1 = qn.to(DEV, dtype).requires_grad_(True)
+    d1 = dn.to(DEV, dtype).requires_grad_(True)
+    q2 = q1.detach().clone().requires_grad_(True)
+    d2 = d1.detach().clone().requires_grad_(True)
+    fused = maxsim.contrastive_loss(q1, d1, off, targets, temperature=temperature)
+    (fused * 3.0).backward()
+    plain = torch.nn.functional.cross_entropy(
+        maxsim.score_contrastive_train(q2, d2, off) / temperature, targets)
+    (plain * 3.0).backward()
+    torch.testing.assert_close(fused, plain, rtol=1e-5, atol=1e-5)
+    tol = dict(rtol=2e-2, atol=2e-2) if dtype != torch.float32 else dict(rtol=1e-4, atol=1e-5)
+    scale = max(1.0, float(q2.grad.float().abs().max()))
+    torch.testing.assert_close(q1.grad.float() / scale, q2.grad.float() / scale, **tol)
+    scale = max(1.0, float(d2.grad.float().abs().max()))
+    torch.testing.assert_close(d1.grad.float() / scale, d2.grad.float() / scale, **tol)
+    # default targets are the diagonal
+    a = maxsim.contrastive_loss(q1.detach(), d1.detach(), off)
+    b = torch.nn.functional.cross_entropy(maxsim.score_contrastive(q1.detach(), d1.detach(), off),
+                                          torch.arange(Nq, device=DEV))
+    torch.testing.assert_close(a, b, rtol=1e-5, atol=1e-5)
+    with pytest.raises(ValueError, match="temperature"):
+        maxsim.contrastive_loss(q1, d1, off, temperature=0.0)
+    with pytest.raises(ValueError, match="targets"):
+        maxsim.contrastive_loss(q1, d1, off, targets[:3])
