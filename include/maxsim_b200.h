@@ -70,8 +70,9 @@ MAXSIM_API int maxsim_b200_device_status(void* stream);
 MAXSIM_API int64_t maxsim_b200_launch_count(void);
 /* Selects the forward implementation: 0 = automatic, 1 = force the portable
  * SIMT kernel, 2 = force the warp-MMA streaming kernel where eligible,
- * 3 = force the tcgen05 kernel where eligible, 5 = force its alternative
- * M = 512 configuration.  For tests and profiling. */
+ * 3 = force the tcgen05 kernel where eligible, 5 / 6 = force its alternative
+ * configurations (M = 512 with 64-token tiles / two CTAs per SM).  For tests
+ * and profiling. */
 MAXSIM_API void maxsim_b200_set_forward_path(int path);
 
 /* Host-side validation helper (no reference counterpart: the reference copies

@@ -65,11 +65,15 @@ struct Cfg {
   static constexpr int kBBoxBytes = BN * 128;          // one BN-row x 64-element box
   static constexpr int kBTileBytes = 2 * kBBoxBytes;
   static constexpr int kATileBytes = 2 * kABoxBytes;   // 32 KB per accumulator
-  static constexpr int kBStages = 4;
+  // <2, 64> is the two-CTAs-per-SM configuration: half the shared memory and
+  // half the TMEM columns per CTA, so two CTAs (16 epilogue warps) share an SM.
+  static constexpr bool kTwoPerSm = (MSUB == 2 && BN == 64);
+  static constexpr int kBStages = kTwoPerSm ? 2 : 4;
+  static constexpr int kMinBlocks = kTwoPerSm ? 2 : 1;
   static constexpr size_t kSmemA = (size_t)MSUB * kATileBytes;
   static constexpr size_t kSmemB = (size_t)kBStages * kBTileBytes;
   static constexpr size_t kSmemBytes = kSmemA + kSmemB + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr bool kPrefetch = (MSUB <= 2);  // second TMEM register buffer only if registers allow
+  static constexpr bool kPrefetch = (MSUB <= 2) && !kTwoPerSm;  // second TMEM register buffer only if registers allow
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
   static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile tokens");
 };
@@ -350,7 +354,7 @@ struct Params {
 };
 
 template <bool ARGMAX, int MSUB, int BN>
-__global__ void __launch_bounds__(Cfg<MSUB, BN>::kThreads, 1)
+__global__ void __launch_bounds__(Cfg<MSUB, BN>::kThreads, Cfg<MSUB, BN>::kMinBlocks)
 fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_d,
                 const Params P) {
   using C = Cfg<MSUB, BN>;
@@ -722,16 +726,20 @@ int launch_tc05_cfg(const PairTable& t, float* scores, int32_t* argmax, int dtyp
       return -3;
     if (track) configured[dev].store(1, std::memory_order_release);
   }
-  const int grid = (int)(n_items < sms ? n_items : sms);
+  const int64_t slots = (int64_t)sms * C::kMinBlocks;
+  const int grid = (int)(n_items < slots ? n_items : slots);
   kern<<<grid, C::kThreads, C::kSmemBytes, st>>>(tm_q, tm_d, P);
   return 0;
 }
 
-// `wide` selects the M = 512 configuration (16 queries per CTA).
+// variant 0: M = 256, 128-token tiles, one CTA per SM (default)
+// variant 1: M = 512, 64-token tiles, 16 epilogue warps
+// variant 2: M = 256, 64-token tiles, two CTAs per SM
 template <bool ARGMAX>
 int launch_tc05(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
-                cudaStream_t st, bool wide) {
-  if (wide) return launch_tc05_cfg<ARGMAX, 4, 64>(t, scores, argmax, dtype, sms, st);
+                cudaStream_t st, int variant) {
+  if (variant == 1) return launch_tc05_cfg<ARGMAX, 4, 64>(t, scores, argmax, dtype, sms, st);
+  if (variant == 2) return launch_tc05_cfg<ARGMAX, 2, 64>(t, scores, argmax, dtype, sms, st);
   return launch_tc05_cfg<ARGMAX, 2, 128>(t, scores, argmax, dtype, sms, st);
 }
 

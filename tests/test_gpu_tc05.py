@@ -56,7 +56,7 @@ SHAPES = [
 
 @pytest.mark.parametrize("Nq,d_lens", SHAPES)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("path", [3, 5])  # 3: M = 256 (default), 5: M = 512 with 64-token tiles
+@pytest.mark.parametrize("path", [3, 5, 6])  # 3: default, 5: M = 512 / 64-token tiles, 6: two CTAs per SM
 def test_tc05_matches_oracle(Nq, d_lens, dtype, path):
     _ops.set_forward_path(path)
     q, d, off = _make(Nq, d_lens, dtype, 11)
