@@ -273,14 +273,42 @@ def bench_train_steps(dev, peaks, full: bool):
     for _ in range(5):
         step2_fused()
     t_fused = statistics.median(_event_ms(step2_fused, 30)) - t_flush
+    # the same step captured once in a CUDA graph and replayed (launch overhead removed)
+    t_graph = None
+    try:
+        def graph_body():
+            loss = maxsim.contrastive_loss(q, d, off)
+            return torch.autograd.grad(loss, (q, d))
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                graph_body()
+        torch.cuda.current_stream().wait_stream(side)
+        cg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(cg):
+            graph_body()
+
+        def step2_graph():
+            flush.zero_()
+            cg.replay()
+
+        for _ in range(5):
+            step2_graph()
+        t_graph = statistics.median(_event_ms(step2_graph, 30)) - t_flush
+    except Exception as exc:  # report, do not fail the benchmark
+        t_graph = f"unavailable: {type(exc).__name__}"
     lens = np.diff(wl.document_offsets).astype(np.int64)
     flops = 2 * 128 * q.shape[0] * 32 * int(lens.sum()) + 4 * 128 * q.shape[0] * lens.shape[0] * 32
     out["c2_contrastive_train_bf16"] = {
         "ms_per_step": t_all - t_flush, "pairs_per_s": q.shape[0] * lens.shape[0] / ((t_all - t_flush) * 1e-3),
         "tensor_frac": flops / ((t_all - t_flush) * 1e-3) / (peaks["bf16_tflops"] * 1e12),
         "ms_per_step_fused_loss": t_fused,
+        "ms_per_step_cuda_graph": t_graph,
         "note": "Nq=Nb=64; L2 flushed between steps (flush time subtracted); launch-latency bound; "
-                "fused_loss = contrastive_loss() instead of score_contrastive_train + torch cross_entropy",
+                "fused_loss = contrastive_loss() instead of score_contrastive_train + torch cross_entropy; "
+                "cuda_graph = that step (loss + both gradients) captured once and replayed",
     }
     # config 1: padded rerank forward + argmax, fp32 (512 pairs; launch-latency bound)
     wl1 = W.c1_padded_rerank_fp32()

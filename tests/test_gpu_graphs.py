@@ -1,0 +1,77 @@
+"""The operators inside CUDA graphs: every kernel is launched on the caller's
+stream with caller-visible allocations only, and an index tensor that was
+validated once is not synchronised on again, so a rerank call or a whole
+contrastive train step can be captured and replayed."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import maxsim_b200 as maxsim
+from maxsim_b200 import _ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def test_rerank_call_replays_from_a_graph():
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(8, 32, 128, generator=g).to(DEV, torch.float16)
+    d = torch.randn(8, 40, 120, 128, generator=g).to(DEV, torch.float16)
+    qlen = torch.randint(20, 33, (8,), generator=g, dtype=torch.int32).to(DEV)
+    dlen = torch.randint(16, 121, (8, 40), generator=g, dtype=torch.int32).to(DEV)
+    eager = maxsim.score_candidates_padded(q, d, qlen, dlen)  # also validates qlen / dlen once
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            maxsim.score_candidates_padded(q, d, qlen, dlen)
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = maxsim.score_candidates_padded(q, d, qlen, dlen)
+    d.copy_(torch.randn(d.shape, generator=g).to(DEV, torch.float16))  # new candidates, same buffers
+    graph.replay()
+    torch.cuda.synchronize()
+    assert not torch.equal(out, eager)
+    assert torch.equal(out, maxsim.score_candidates_padded(q, d, qlen, dlen))
+    assert _ops.device_status() == 0
+
+
+def test_contrastive_train_step_replays_from_a_graph():
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(16, 32, 128, generator=g).to(DEV, torch.bfloat16).requires_grad_(True)
+    d = torch.randn(16 * 50, 128, generator=g).to(DEV, torch.bfloat16).requires_grad_(True)
+    off = torch.arange(0, 16 * 50 + 1, 50, dtype=torch.int32, device=DEV)
+
+    def step():
+        loss = maxsim.contrastive_loss(q, d, off, temperature=0.5)
+        gq, gd = torch.autograd.grad(loss, (q, d))
+        return loss, gq, gd
+
+    # Warm up on a side stream and capture there.  (Running the step on the
+    # default stream first would leave autograd nodes bound to that stream,
+    # which a capture may not touch.)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        loss, gq, gd = step()
+    graph.replay()
+    torch.cuda.synchronize()
+    want = [t.detach().clone() for t in step()]
+    torch.testing.assert_close(loss, want[0], rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(gq, want[1], rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(gd.float(), want[2].float(), rtol=2e-2, atol=1e-4)  # summation order
+    with torch.no_grad():
+        q.copy_(torch.randn(q.shape, generator=g).to(DEV, torch.bfloat16))
+    graph.replay()
+    torch.cuda.synchronize()
+    fresh = step()
+    torch.testing.assert_close(loss, fresh[0].detach(), rtol=1e-6, atol=1e-6)
+    assert _ops.device_status() == 0
