@@ -97,6 +97,33 @@ MAXSIM_API int maxsim_b200_contrastive_ce(const float* scores, const int64_t* ta
                                           int64_t Nq, int64_t Nb, float temperature,
                                           float grad_scale, void* stream);
 
+/* Either side of the operators (no compiled reference counterpart: the
+ * reference's callers pack with Python slicing and torch.cat, README.md:185-192,
+ * or with a boolean-mask gather, torch-ext/maxsim/__init__.py:516-620, and
+ * rank with argsort, README.md:270-274).
+ *
+ * offsets_from_lengths: offsets[0] = 0, offsets[n+1] = offsets[n] +
+ * clamp(lengths[n], 0, L_max), int32; *total (device, may be NULL) receives
+ * the 64-bit sum.
+ * pack_rows: packed[offsets[n] + j] = padded[n, j] for j < offsets[n+1] -
+ * offsets[n]; rows are row_bytes bytes of any element type.
+ * unpack_rows: the reverse copy; padded[n, j] = 0 for j beyond the segment.
+ * Rows at or beyond packed_rows are never read or written.
+ * topk_rows: for each of `rows` score rows of `cols` floats the k best
+ * entries, best first, equal scores by ascending index, NaN above +inf;
+ * values [rows, k] float, indices [rows, k] int64.  cols <= 16384. */
+MAXSIM_API int maxsim_b200_offsets_from_lengths(const int32_t* lengths, int64_t n,
+                                                int64_t L_max, int32_t* offsets,
+                                                int64_t* total, void* stream);
+MAXSIM_API int maxsim_b200_pack_rows(const void* padded, const int32_t* offsets, void* packed,
+                                     int64_t n_segments, int64_t L_max, int64_t row_bytes,
+                                     int64_t packed_rows, void* stream);
+MAXSIM_API int maxsim_b200_unpack_rows(const void* packed, const int32_t* offsets, void* padded,
+                                       int64_t n_segments, int64_t L_max, int64_t row_bytes,
+                                       int64_t packed_rows, void* stream);
+MAXSIM_API int maxsim_b200_topk_rows(const float* scores, int64_t rows, int64_t cols, int64_t k,
+                                     float* values, int64_t* indices, void* stream);
+
 /* ------------------------------------------------------------------------
  * Packed pair grids.
  * queries [total_q_tokens, dim], query_offsets [n_queries+1],

@@ -41,6 +41,10 @@ _SIGNATURES = {
     "maxsim_b200_set_forward_path": (None, [c_int]),
     "maxsim_b200_layout_stats": (c_int, [_P, _I64, _P, _I64, c_int, _P, _P]),
     "maxsim_b200_contrastive_ce": (c_int, [_P] * 4 + [_I64] * 2 + [ctypes.c_float] * 2 + [_P]),
+    "maxsim_b200_offsets_from_lengths": (c_int, [_P, _I64, _I64, _P, _P, _P]),
+    "maxsim_b200_pack_rows": (c_int, [_P] * 3 + [_I64] * 4 + [_P]),
+    "maxsim_b200_unpack_rows": (c_int, [_P] * 3 + [_I64] * 4 + [_P]),
+    "maxsim_b200_topk_rows": (c_int, [_P] + [_I64] * 3 + [_P] * 3),
     "maxsim_forward": (c_int, [_P] * 7 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_forward_with_argmax": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_backward": (c_int, [_P] * 10 + [_I64] * 7 + [c_int, _P]),
@@ -141,6 +145,70 @@ def contrastive_ce(scores: torch.Tensor, targets: torch.Tensor, temperature: flo
             s.shape[0], s.shape[1], float(temperature), float(grad_scale), _stream_ptr())
     _check(rc, "maxsim_b200_contrastive_ce")
     return loss_rows, dscore
+
+
+def offsets_from_lengths(lengths: torch.Tensor, L_max: int):
+    """``lengths [N]`` (CUDA, integer) -> ``(offsets [N+1] int32, total [1] int64)``,
+    both on the device; lengths are clamped to ``[0, L_max]``."""
+    dev = _require_cuda(lengths)
+    ln = _i32(lengths.reshape(-1))
+    offsets = torch.empty((ln.shape[0] + 1,), dtype=torch.int32, device=dev)
+    total = torch.empty((1,), dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_b200_offsets_from_lengths(
+            _ptr(ln), ln.shape[0], int(L_max), offsets.data_ptr(), total.data_ptr(), _stream_ptr())
+    _check(rc, "maxsim_b200_offsets_from_lengths")
+    return offsets, total
+
+
+def pack_rows(padded: torch.Tensor, offsets: torch.Tensor, packed_rows: int) -> torch.Tensor:
+    """``padded [N, L_max, ...]`` -> ``packed [packed_rows, ...]``: segment ``n`` contributes its
+    first ``offsets[n+1] - offsets[n]`` rows."""
+    dev = _require_cuda(padded, offsets)
+    src = padded.contiguous()
+    off = _i32(offsets)
+    n, L = src.shape[0], src.shape[1]
+    packed = torch.empty((int(packed_rows),) + tuple(src.shape[2:]), dtype=src.dtype, device=dev)
+    row_bytes = (src[0, 0].numel() if n and L else 1) * src.element_size()
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_b200_pack_rows(
+            _ptr(src), _ptr(off), _ptr(packed), n, L, row_bytes, int(packed_rows), _stream_ptr())
+    _check(rc, "maxsim_b200_pack_rows")
+    return packed
+
+
+def unpack_rows(packed: torch.Tensor, offsets: torch.Tensor, L_max: int) -> torch.Tensor:
+    """``packed [T, ...]`` -> ``padded [N, L_max, ...]`` with zeros beyond each segment."""
+    dev = _require_cuda(packed, offsets)
+    src = packed.contiguous()
+    off = _i32(offsets)
+    n = off.shape[0] - 1
+    padded = torch.empty((n, int(L_max)) + tuple(src.shape[1:]), dtype=src.dtype, device=dev)
+    row_bytes = 1
+    for extent in src.shape[1:]:
+        row_bytes *= extent
+    row_bytes *= src.element_size()
+    if row_bytes == 0:
+        return padded
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_b200_unpack_rows(
+            _ptr(src), _ptr(off), _ptr(padded), n, int(L_max), row_bytes, src.shape[0],
+            _stream_ptr())
+    _check(rc, "maxsim_b200_unpack_rows")
+    return padded
+
+
+def topk_rows(scores: torch.Tensor, k: int):
+    """``scores [rows, cols]`` fp32 -> ``(values [rows, k] fp32, indices [rows, k] int64)``."""
+    dev = _require_cuda(scores)
+    s = scores.contiguous().to(torch.float32)
+    values = torch.empty((s.shape[0], int(k)), dtype=torch.float32, device=dev)
+    indices = torch.empty((s.shape[0], int(k)), dtype=torch.int64, device=dev)
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_b200_topk_rows(
+            _ptr(s), s.shape[0], s.shape[1], int(k), _ptr(values), _ptr(indices), _stream_ptr())
+    _check(rc, "maxsim_b200_topk_rows")
+    return values, indices
 
 
 def _stream_ptr() -> int:

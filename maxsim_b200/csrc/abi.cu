@@ -14,6 +14,7 @@
 #include "fwd_tc05.cuh"
 #include "layout_stats.cuh"
 #include "loss.cuh"
+#include "pack.cuh"
 
 namespace maxsim {
 
@@ -297,6 +298,37 @@ PairTable contrastive_table(const void* q, const void* d, const int32_t* doff, i
 
 bool fits_i32(int64_t v) { return v >= 0 && v < (1ll << 31); }
 
+template <bool TO_PACKED>
+int run_segment_copy(const void* src, void* dst, const int32_t* offsets, int64_t n_segments,
+                     int64_t L_max, int64_t row_bytes, int64_t packed_rows, void* stream) {
+  if (n_segments < 0 || L_max < 0 || row_bytes <= 0 || packed_rows < 0 || !fits_i32(L_max))
+    return fail(MAXSIM_EINVAL, "sizes must be >= 0 (row_bytes > 0) and L_max must fit int32");
+  if (n_segments == 0 || L_max == 0) return MAXSIM_OK;
+  if (!src || !dst || !offsets) return fail(MAXSIM_EINVAL, "null pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int sms = sm_count();
+  const int64_t slab_bytes = L_max * row_bytes;
+  int64_t gy = (slab_bytes + 16 * 4 * kCopyThreads - 1) / (16 * 4 * kCopyThreads);
+  gy = gy < 1 ? 1 : (gy > 8 ? 8 : gy);
+  int64_t gx = n_segments;
+  const int64_t cap = (int64_t)sms * 64;
+  if (gx * gy > cap) gx = cap / gy;
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  const bool a16 = aligned16(src) && aligned16(dst) && row_bytes % 16 == 0;
+  const bool a4 = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 3u) == 0 &&
+                  row_bytes % 4 == 0;
+  if (a16)
+    segment_copy_kernel<uint4, TO_PACKED><<<grid, kCopyThreads, 0, st>>>(
+        src, dst, offsets, n_segments, (int)L_max, row_bytes, packed_rows);
+  else if (a4)
+    segment_copy_kernel<uint32_t, TO_PACKED><<<grid, kCopyThreads, 0, st>>>(
+        src, dst, offsets, n_segments, (int)L_max, row_bytes, packed_rows);
+  else
+    segment_copy_kernel<uint8_t, TO_PACKED><<<grid, kCopyThreads, 0, st>>>(
+        src, dst, offsets, n_segments, (int)L_max, row_bytes, packed_rows);
+  return launch_check("segment_copy_kernel");
+}
+
 }  // namespace
 }  // namespace maxsim
 
@@ -344,6 +376,49 @@ int maxsim_b200_contrastive_ce(const float* scores, const int64_t* targets, floa
   contrastive_ce_kernel<<<(unsigned)Nq, kLossThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       scores, targets, loss_rows, dscore, (int)Nb, 1.0f / temperature, grad_scale);
   return launch_check("contrastive_ce_kernel");
+}
+
+int maxsim_b200_offsets_from_lengths(const int32_t* lengths, int64_t n, int64_t L_max,
+                                     int32_t* offsets, int64_t* total, void* stream) {
+  if (n < 0 || L_max < 0 || !fits_i32(L_max)) return fail(MAXSIM_EINVAL, "sizes must be >= 0 and fit int32");
+  if (!offsets || (n > 0 && !lengths)) return fail(MAXSIM_EINVAL, "null pointer argument");
+  offsets_from_lengths_kernel<<<1, kScanThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      lengths, n, (int)L_max, offsets, reinterpret_cast<long long*>(total));
+  return launch_check("offsets_from_lengths_kernel");
+}
+
+int maxsim_b200_pack_rows(const void* padded, const int32_t* offsets, void* packed,
+                          int64_t n_segments, int64_t L_max, int64_t row_bytes,
+                          int64_t packed_rows, void* stream) {
+  return run_segment_copy<true>(padded, packed, offsets, n_segments, L_max, row_bytes, packed_rows,
+                                stream);
+}
+
+int maxsim_b200_unpack_rows(const void* packed, const int32_t* offsets, void* padded,
+                            int64_t n_segments, int64_t L_max, int64_t row_bytes,
+                            int64_t packed_rows, void* stream) {
+  return run_segment_copy<false>(packed, padded, offsets, n_segments, L_max, row_bytes, packed_rows,
+                                 stream);
+}
+
+int maxsim_b200_topk_rows(const float* scores, int64_t rows, int64_t cols, int64_t k,
+                          float* values, int64_t* indices, void* stream) {
+  if (rows < 0 || cols < 0 || k < 0 || k > cols) return fail(MAXSIM_EINVAL, "need 0 <= k <= cols");
+  if (cols > kTopkMaxCols)
+    return fail(MAXSIM_EUNSUPPORTED, "topk_rows sorts at most %d columns per row; got %lld",
+                kTopkMaxCols, (long long)cols);
+  if (rows >= (1ll << 31)) return fail(MAXSIM_EINVAL, "too many rows");
+  if (rows == 0 || k == 0) return MAXSIM_OK;
+  if (!scores || !values || !indices) return fail(MAXSIM_EINVAL, "null pointer argument");
+  int n_pow2 = 2;
+  while (n_pow2 < cols) n_pow2 <<= 1;
+  const size_t smem = (size_t)n_pow2 * sizeof(unsigned long long);
+  static std::atomic<unsigned char> configured[kMaxDevices];
+  if (int rc = ensure_smem(topk_rows_kernel, (size_t)kTopkMaxCols * sizeof(unsigned long long), configured))
+    return rc;
+  topk_rows_kernel<<<(unsigned)rows, kTopkThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      scores, cols, n_pow2, (int)k, values, reinterpret_cast<long long*>(indices));
+  return launch_check("topk_rows_kernel");
 }
 
 int maxsim_forward(const void* queries, const int32_t* query_offsets, const void* documents,

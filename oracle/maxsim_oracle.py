@@ -290,3 +290,51 @@ def argmax_mismatch_allowed(got, want, gaps, tol):
     got = np.asarray(got)
     want = np.asarray(want)
     return (got == want) | (np.asarray(gaps) < tol)
+
+
+# ---------------------------------------------------------------------------
+# Either side of the operators: packing and ranking, as the reference's callers
+# write them.
+# ---------------------------------------------------------------------------
+
+def pack_padded(padded, lengths):
+    """``padded [N, L_max, ...]`` + prefix ``lengths [N]`` -> ``(packed [T, ...],
+    offsets [N+1] int32)``: the slices ``padded[n, :lengths[n]]`` back to back
+    (README.md:185-192 of the reference; the mask gather of
+    torch-ext/maxsim/__init__.py:594-606 gives the same rows in the same order)."""
+    padded = np.asarray(padded)
+    lengths = np.asarray(lengths).astype(np.int64)
+    offsets = np.zeros(lengths.shape[0] + 1, dtype=np.int64)
+    np.cumsum(lengths, out=offsets[1:])
+    parts = [padded[n, :lengths[n]] for n in range(lengths.shape[0])]
+    packed = np.concatenate(parts, axis=0) if parts else padded.reshape((0,) + padded.shape[2:])
+    return packed, offsets.astype(np.int32)
+
+
+def unpack_packed(packed, offsets, L_max):
+    """The reverse copy: ``out[n, j] = packed[offsets[n] + j]`` for ``j`` inside
+    segment ``n`` (truncated at ``L_max``), zero elsewhere."""
+    packed = np.asarray(packed)
+    offsets = np.asarray(offsets).astype(np.int64)
+    n_seg = offsets.shape[0] - 1
+    out = np.zeros((n_seg, L_max) + packed.shape[1:], dtype=packed.dtype)
+    for n in range(n_seg):
+        ln = min(int(offsets[n + 1] - offsets[n]), L_max)
+        out[n, :ln] = packed[offsets[n]:offsets[n] + ln]
+    return out
+
+
+def rank_rows(scores, k):
+    """``scores [B, C]`` -> ``(values [B, k], indices [B, k] int64)``: each row in
+    descending order (README.md:270-274 of the reference ranks candidates with
+    ``argsort(descending=True)``), equal scores by ascending index, NaN first."""
+    scores = np.asarray(scores, dtype=np.float32)
+    B, C = scores.shape
+    idx = np.empty((B, k), dtype=np.int64)
+    for b in range(B):
+        row = scores[b]
+        order = sorted(range(C), key=lambda j: (0 if np.isnan(row[j]) else 1,
+                                                -float(row[j]) if not np.isnan(row[j]) else 0.0, j))
+        idx[b] = order[:k]
+    vals = np.take_along_axis(scores, idx, axis=1) if k else np.empty((B, 0), np.float32)
+    return vals, idx
