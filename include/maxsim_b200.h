@@ -166,6 +166,58 @@ MAXSIM_API int maxsim_packed_backward(
     int64_t total_q_tokens, int64_t total_d_tokens,
     int64_t dim, int64_t max_q_len, int dtype, void* stream);
 
+/* Grouping of a packed pair list (no reference counterpart: the reference
+ * works through the list in list order, one CTA per entry, and routes
+ * gradients with global atomics, maxsim_cuda/maxsim.cu:70-126, 1933-2010,
+ * 2122-2169).
+ *
+ * group_pairs sorts the pair indices by an id (counting sort): order [n_pairs]
+ * receives a permutation of [0, n_pairs) in which pairs with the same id are
+ * adjacent, ids ascending; ends [n_bins] is scratch memory during the call and
+ * afterwards holds, for every id b, the end of its group: the group of b is
+ * order[(b ? ends[b-1] : 0) .. ends[b]).  Call it with pair_document_ids /
+ * n_documents and with pair_query_ids / n_queries.
+ *
+ * The *_ordered forward operators are the packed forward operators given the
+ * by-document permutation as pair_order (NULL = list order): they visit the
+ * pairs in that order, so that a document named by several pairs is read from
+ * HBM once and found in L2 afterwards.  maxsim_packed_backward_grouped is
+ * maxsim_packed_backward given both groupings: grad_queries is gathered per
+ * query and grad_documents is owned by one warp per document, so there is no
+ * zero-fill pass, no atomic and no run-to-run difference in the sums' order
+ * beyond the order inside a group.  It needs dim % 8 == 0 and 16-byte aligned
+ * tensors; otherwise, or with a NULL grouping, it falls back to the plain
+ * operator.  Results are those of the plain operators. */
+MAXSIM_API int maxsim_b200_group_pairs(const int32_t* ids, int64_t n_pairs, int64_t n_bins,
+                                       int32_t* ends, int32_t* order, void* stream);
+MAXSIM_API int maxsim_forward_ordered(const void* queries, const int32_t* query_offsets,
+                   const void* documents, const int32_t* document_offsets,
+                   const int32_t* pair_query_ids, const int32_t* pair_document_ids,
+                   const int32_t* pair_order, float* scores,
+                   int64_t n_pairs, int64_t n_queries, int64_t n_documents,
+                   int64_t total_q_tokens, int64_t total_d_tokens,
+                   int64_t dim, int64_t max_q_len, int dtype, void* stream);
+MAXSIM_API int maxsim_packed_forward_with_argmax_ordered(
+    const void* queries, const int32_t* query_offsets,
+    const void* documents, const int32_t* document_offsets,
+    const int32_t* pair_query_ids, const int32_t* pair_document_ids,
+    const int32_t* pair_order, float* scores, int32_t* argmax,
+    int64_t n_pairs, int64_t n_queries, int64_t n_documents,
+    int64_t total_q_tokens, int64_t total_d_tokens,
+    int64_t dim, int64_t max_q_len, int dtype, void* stream);
+MAXSIM_API int maxsim_packed_backward_grouped(
+    const float* dscore,
+    const void* queries, const int32_t* query_offsets,
+    const void* documents, const int32_t* document_offsets,
+    const int32_t* pair_query_ids, const int32_t* pair_document_ids,
+    const int32_t* order_by_query, const int32_t* ends_by_query,
+    const int32_t* order_by_document, const int32_t* ends_by_document,
+    const int32_t* argmax,
+    float* grad_queries, float* grad_documents,
+    int64_t n_pairs, int64_t n_queries, int64_t n_documents,
+    int64_t total_q_tokens, int64_t total_d_tokens,
+    int64_t dim, int64_t max_q_len, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------
  * Padded candidates.
  * queries [B*Lq_max, dim], query_lengths [B],

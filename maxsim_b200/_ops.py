@@ -18,6 +18,7 @@ from __future__ import annotations
 import ctypes
 import os
 import types
+import weakref
 from pathlib import Path
 from ctypes import c_char_p, c_int, c_int64, c_void_p
 from typing import Tuple
@@ -45,6 +46,10 @@ _SIGNATURES = {
     "maxsim_b200_pack_rows": (c_int, [_P] * 3 + [_I64] * 4 + [_P]),
     "maxsim_b200_unpack_rows": (c_int, [_P] * 3 + [_I64] * 4 + [_P]),
     "maxsim_b200_topk_rows": (c_int, [_P] + [_I64] * 3 + [_P] * 3),
+    "maxsim_b200_group_pairs": (c_int, [_P, _I64, _I64, _P, _P, _P]),
+    "maxsim_forward_ordered": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
+    "maxsim_packed_forward_with_argmax_ordered": (c_int, [_P] * 9 + [_I64] * 7 + [c_int, _P]),
+    "maxsim_packed_backward_grouped": (c_int, [_P] * 14 + [_I64] * 7 + [c_int, _P]),
     "maxsim_forward": (c_int, [_P] * 7 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_forward_with_argmax": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_backward": (c_int, [_P] * 10 + [_I64] * 7 + [c_int, _P]),
@@ -257,6 +262,59 @@ def _same_float(q: torch.Tensor, d: torch.Tensor) -> None:
 # packed
 # ---------------------------------------------------------------------------
 
+# Pair lists at least this long are grouped by document (forward with argmax,
+# backward) and by query (backward).
+GROUP_MIN_PAIRS = 2048
+_group_enabled = True
+_GROUP_CACHE = {}
+_GROUP_CACHE_LIMIT = 32
+
+
+def set_pair_grouping(enabled: bool) -> None:
+    """Switch the grouping of packed pair lists on or off (for A/B timing)."""
+    global _group_enabled
+    _group_enabled = bool(enabled)
+
+
+def group_pairs(ids: torch.Tensor, n_bins: int):
+    """Counting sort of a pair list by ``ids`` (document or query ids in
+    ``[0, n_bins)``): returns ``(order, ends)``, int32 on the device --
+    ``order`` a permutation of ``range(n_pairs)`` with equal ids adjacent,
+    ``ends[b]`` the end of id ``b``'s group in it."""
+    dev = _require_cuda(ids)
+    flat = _i32(ids.reshape(-1))
+    order = torch.empty((flat.shape[0],), dtype=torch.int32, device=dev)
+    ends = torch.empty((max(int(n_bins), 1),), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_b200_group_pairs(
+            _ptr(flat), flat.shape[0], max(int(n_bins), 1), ends.data_ptr(), _ptr(order),
+            _stream_ptr())
+    _check(rc, "maxsim_b200_group_pairs")
+    return order, ends
+
+
+def _groups(key: torch.Tensor, ids32: torch.Tensor, n_bins: int, build: bool = True):
+    """``(order, ends)`` of a pair-id tensor, or None.  ``key`` is the tensor
+    object the caller passed: its grouping is remembered until the tensor is
+    written to or dies.  With ``build=False`` only a remembered grouping is
+    returned."""
+    if not _group_enabled or ids32.shape[0] < GROUP_MIN_PAIRS or n_bins <= 0:
+        return None
+    ent = _GROUP_CACHE.get(id(key))
+    if ent is not None and ent[0]() is key and ent[1] == key._version and ent[2] == n_bins:
+        return ent[3]
+    if not build:
+        return None
+    groups = group_pairs(ids32, n_bins)
+    if len(_GROUP_CACHE) >= _GROUP_CACHE_LIMIT:
+        _GROUP_CACHE.clear()
+    try:
+        _GROUP_CACHE[id(key)] = (weakref.ref(key), key._version, n_bins, groups)
+    except TypeError:
+        pass
+    return groups
+
+
 def _packed_args(queries, query_offsets, documents, document_offsets,
                  pair_query_ids, pair_document_ids):
     if queries.dim() != 2 or documents.dim() != 2:
@@ -287,8 +345,11 @@ def maxsim_forward(queries, query_offsets, documents, document_offsets,
     if max_q_len <= 0:
         raise RuntimeError(f"max_q_len must be > 0; got {max_q_len}")
     with torch.cuda.device(dev):
-        rc = load_library().maxsim_forward(
-            _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd), _ptr(scores),
+        # score-only calls use the document order only if it is already known
+        by_doc = _groups(pair_document_ids, pd, doff.shape[0] - 1, build=False)
+        rc = load_library().maxsim_forward_ordered(
+            _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd),
+            _ptr(by_doc[0]) if by_doc is not None else 0, _ptr(scores),
             n_pairs, qoff.shape[0] - 1, doff.shape[0] - 1, q.shape[0], d.shape[0],
             q.shape[1], max_q_len, _code(q), _stream_ptr())
     _check(rc, "maxsim_forward")
@@ -311,9 +372,10 @@ def maxsim_packed_forward_with_argmax(queries, query_offsets, documents, documen
     if n_pairs == 0:
         return scores, argmax
     with torch.cuda.device(dev):
-        rc = load_library().maxsim_packed_forward_with_argmax(
+        by_doc = _groups(pair_document_ids, pd, doff.shape[0] - 1)
+        rc = load_library().maxsim_packed_forward_with_argmax_ordered(
             _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd),
-            _ptr(scores), _ptr(argmax),
+            _ptr(by_doc[0]) if by_doc is not None else 0, _ptr(scores), _ptr(argmax),
             n_pairs, qoff.shape[0] - 1, doff.shape[0] - 1, q.shape[0], d.shape[0],
             q.shape[1], max_q_len, _code(q), _stream_ptr())
     _check(rc, "maxsim_packed_forward_with_argmax")
@@ -338,8 +400,13 @@ def maxsim_packed_backward(dscore, queries, query_offsets, documents, document_o
     dq = torch.empty(q.shape, dtype=torch.float32, device=dev)
     dd = torch.empty(d.shape, dtype=torch.float32, device=dev)
     with torch.cuda.device(dev):
-        rc = load_library().maxsim_packed_backward(
-            _ptr(g), _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd), _ptr(a),
+        by_doc = _groups(pair_document_ids, pd, doff.shape[0] - 1)
+        by_query = _groups(pair_query_ids, pq, qoff.shape[0] - 1)
+        grouped = by_doc is not None and by_query is not None
+        rc = load_library().maxsim_packed_backward_grouped(
+            _ptr(g), _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd),
+            _ptr(by_query[0]) if grouped else 0, by_query[1].data_ptr() if grouped else 0,
+            _ptr(by_doc[0]) if grouped else 0, by_doc[1].data_ptr() if grouped else 0, _ptr(a),
             _ptr(dq), _ptr(dd),
             n_pairs, qoff.shape[0] - 1, doff.shape[0] - 1, q.shape[0], d.shape[0],
             q.shape[1], max(max_q_len, 1), _code(q), _stream_ptr())

@@ -12,6 +12,7 @@
 #include "fwd_mma.cuh"
 #include "fwd_simt.cuh"
 #include "fwd_tc05.cuh"
+#include "group.cuh"
 #include "layout_stats.cuh"
 #include "loss.cuh"
 #include "pack.cuh"
@@ -109,6 +110,7 @@ int launch_mma_dim(const PairTable& t, float* scores, int32_t* argmax, cudaStrea
   int ppc = (int)(t.n_pairs / (warps_full * 4));
   if (ppc < 1) ppc = 1;
   if (ppc > 8) ppc = 8;
+  if (t.order && ppc > 2) ppc = 2;  // same-document pairs to different warps at about the same time
   const int64_t n_chunks = (t.n_pairs + ppc - 1) / ppc;
   int64_t grid = (n_chunks + kMmaWarps - 1) / kMmaWarps;
   if (grid > sms) grid = sms;
@@ -182,12 +184,29 @@ int run_forward(const PairTable& t, float* scores, int32_t* argmax, int dtype, v
 // ---------------------------------------------------------------------------
 template <typename T, int LAYOUT>
 int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argmax, float* dq,
-                   float* dd, int64_t q_rows, int64_t d_rows, int64_t Nq, cudaStream_t st) {
+                   float* dd, int64_t q_rows, int64_t d_rows, int64_t Nq, cudaStream_t st,
+                   int64_t n_queries, int64_t n_documents) {
   const int dim = t.dim;
   const int vec_ok = (dim % 4 == 0) && aligned16(t.queries) && aligned16(t.documents) &&
                      aligned16(dq) && aligned16(dd);
   const unsigned threads = kBwdWarps * 32;
   if constexpr (LAYOUT == kPacked) {
+    if (t.order_q && vec_ok && dim % 8 == 0 && t.n_pairs > 0 &&
+        n_queries * (int64_t)t.q_slots < (1ll << 33)) {
+      // grouped lists: owner warps, every output row written once
+      if (n_queries > 0) {
+        const int64_t rows = n_queries * (int64_t)t.q_slots;
+        bwd_dq_packed_kernel<T><<<(unsigned)((rows + kBwdWarps - 1) / kBwdWarps), threads, 0, st>>>(
+            t, dscore, argmax, dq, n_queries);
+        if (int rc = launch_check("bwd_dq_packed_kernel")) return rc;
+      }
+      if (n_documents > 0) {
+        bwd_dd_packed_kernel<T><<<(unsigned)((n_documents + kBwdWarps - 1) / kBwdWarps), threads, 0, st>>>(
+            t, dscore, argmax, dd, n_documents);
+        if (int rc = launch_check("bwd_dd_packed_kernel")) return rc;
+      }
+      return MAXSIM_OK;
+    }
     MAXSIM_CUDA(cudaMemsetAsync(dq, 0, (size_t)q_rows * dim * sizeof(float), st));
     MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
     if (t.n_pairs == 0) return MAXSIM_OK;
@@ -247,7 +266,8 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
 
 template <int LAYOUT>
 int run_backward(const PairTable& t, const float* dscore, const int32_t* argmax, float* dq,
-                 float* dd, int64_t q_rows, int64_t d_rows, int64_t Nq, int dtype, void* stream) {
+                 float* dd, int64_t q_rows, int64_t d_rows, int64_t Nq, int dtype, void* stream,
+                 int64_t n_queries = 0, int64_t n_documents = 0) {
   if (!valid_dtype(dtype)) return fail(MAXSIM_EINVAL, "unknown dtype code %d", dtype);
   if (t.dim <= 0 || t.q_slots <= 0 || t.n_pairs < 0 || q_rows < 0 || d_rows < 0)
     return fail(MAXSIM_EINVAL, "sizes must be positive");
@@ -256,18 +276,22 @@ int run_backward(const PairTable& t, const float* dscore, const int32_t* argmax,
     return fail(MAXSIM_EINVAL, "null pointer argument");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
-    case MAXSIM_F32: return run_backward_t<float, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
-    case MAXSIM_F16: return run_backward_t<__half, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
-    default: return run_backward_t<__nv_bfloat16, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
+    case MAXSIM_F32: return run_backward_t<float, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st,
+                                                  n_queries, n_documents);
+    case MAXSIM_F16: return run_backward_t<__half, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st,
+                                                  n_queries, n_documents);
+    default: return run_backward_t<__nv_bfloat16, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st,
+                                                  n_queries, n_documents);
   }
 }
 
 PairTable packed_table(const void* q, const int32_t* qoff, const void* d, const int32_t* doff,
                        const int32_t* pq, const int32_t* pd, int64_t n_pairs, int64_t dim,
-                       int64_t max_q_len, int64_t q_rows, int64_t d_rows) {
+                       int64_t max_q_len, int64_t q_rows, int64_t d_rows,
+                       const int32_t* order = nullptr) {
   PairTable t{};
   t.queries = q; t.documents = d;
-  t.ia = qoff; t.ib = doff; t.ic = pq; t.id = pd;
+  t.ia = qoff; t.ib = doff; t.ic = pq; t.id = pd; t.order = order;
   t.n_pairs = n_pairs; t.dim = (int32_t)dim; t.q_slots = (int32_t)max_q_len;
   t.q_rows = q_rows; t.d_rows = d_rows;
   t.Ld_max = 0; t.C = 1;
@@ -421,20 +445,72 @@ int maxsim_b200_topk_rows(const float* scores, int64_t rows, int64_t cols, int64
   return launch_check("topk_rows_kernel");
 }
 
-int maxsim_forward(const void* queries, const int32_t* query_offsets, const void* documents,
-                   const int32_t* document_offsets, const int32_t* pair_query_ids,
-                   const int32_t* pair_document_ids, float* scores, int64_t n_pairs,
-                   int64_t n_queries, int64_t n_documents, int64_t total_q_tokens,
-                   int64_t total_d_tokens, int64_t dim, int64_t max_q_len, int dtype,
-                   void* stream) {
+int maxsim_b200_group_pairs(const int32_t* pair_document_ids, int64_t n_pairs,
+                            int64_t n_documents, int32_t* bins_scratch, int32_t* order,
+                            void* stream) {
+  if (n_pairs < 0 || n_documents <= 0 || !fits_i32(n_pairs) || !fits_i32(n_documents))
+    return fail(MAXSIM_EINVAL, "n_pairs must be >= 0, n_bins > 0, both within int32");
+  if (!bins_scratch) return fail(MAXSIM_EINVAL, "null pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MAXSIM_CUDA(cudaMemsetAsync(bins_scratch, 0, (size_t)n_documents * sizeof(int32_t), st));
+  if (n_pairs == 0) return MAXSIM_OK;
+  if (!pair_document_ids || !order) return fail(MAXSIM_EINVAL, "null pointer argument");
+  int64_t grid = (n_pairs + kGroupThreads - 1) / kGroupThreads;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (grid > cap) grid = cap;
+  group_count_kernel<<<(unsigned)grid, kGroupThreads, 0, st>>>(pair_document_ids, n_pairs,
+                                                               (int32_t)n_documents, bins_scratch);
+  if (int rc = launch_check("group_count_kernel")) return rc;
+  group_scan_kernel<<<1, kGroupScanThreads, 0, st>>>(bins_scratch, (int32_t)n_documents);
+  if (int rc = launch_check("group_scan_kernel")) return rc;
+  group_scatter_kernel<<<(unsigned)grid, kGroupThreads, 0, st>>>(
+      pair_document_ids, n_pairs, (int32_t)n_documents, bins_scratch, order);
+  return launch_check("group_scatter_kernel");
+}
+
+int maxsim_forward_ordered(const void* queries, const int32_t* query_offsets,
+                           const void* documents, const int32_t* document_offsets,
+                           const int32_t* pair_query_ids, const int32_t* pair_document_ids,
+                           const int32_t* pair_order, float* scores, int64_t n_pairs,
+                           int64_t n_queries, int64_t n_documents, int64_t total_q_tokens,
+                           int64_t total_d_tokens, int64_t dim, int64_t max_q_len, int dtype,
+                           void* stream) {
   (void)n_queries; (void)n_documents;
   if (!fits_i32(dim) || !fits_i32(max_q_len) || !fits_i32(total_q_tokens) || !fits_i32(total_d_tokens))
     return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
   if (max_q_len <= 0) return fail(MAXSIM_EINVAL, "max_q_len must be > 0; got %lld", (long long)max_q_len);
   PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
                              pair_document_ids, n_pairs, dim, max_q_len, total_q_tokens,
-                             total_d_tokens);
+                             total_d_tokens, pair_order);
   return run_forward<kPacked, false>(t, scores, nullptr, dtype, stream);
+}
+
+int maxsim_forward(const void* queries, const int32_t* query_offsets, const void* documents,
+                   const int32_t* document_offsets, const int32_t* pair_query_ids,
+                   const int32_t* pair_document_ids, float* scores, int64_t n_pairs,
+                   int64_t n_queries, int64_t n_documents, int64_t total_q_tokens,
+                   int64_t total_d_tokens, int64_t dim, int64_t max_q_len, int dtype,
+                   void* stream) {
+  return maxsim_forward_ordered(queries, query_offsets, documents, document_offsets,
+                                pair_query_ids, pair_document_ids, nullptr, scores, n_pairs,
+                                n_queries, n_documents, total_q_tokens, total_d_tokens, dim,
+                                max_q_len, dtype, stream);
+}
+
+int maxsim_packed_forward_with_argmax_ordered(
+    const void* queries, const int32_t* query_offsets, const void* documents,
+    const int32_t* document_offsets, const int32_t* pair_query_ids,
+    const int32_t* pair_document_ids, const int32_t* pair_order, float* scores, int32_t* argmax,
+    int64_t n_pairs, int64_t n_queries, int64_t n_documents, int64_t total_q_tokens,
+    int64_t total_d_tokens, int64_t dim, int64_t max_q_len, int dtype, void* stream) {
+  (void)n_queries; (void)n_documents;
+  if (!fits_i32(dim) || !fits_i32(max_q_len) || !fits_i32(total_q_tokens) || !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
+  if (max_q_len <= 0) return fail(MAXSIM_EINVAL, "max_q_len must be > 0; got %lld", (long long)max_q_len);
+  PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
+                             pair_document_ids, n_pairs, dim, max_q_len, total_q_tokens,
+                             total_d_tokens, pair_order);
+  return run_forward<kPacked, true>(t, scores, argmax, dtype, stream);
 }
 
 int maxsim_packed_forward_with_argmax(const void* queries, const int32_t* query_offsets,
@@ -445,14 +521,36 @@ int maxsim_packed_forward_with_argmax(const void* queries, const int32_t* query_
                                       int64_t n_documents, int64_t total_q_tokens,
                                       int64_t total_d_tokens, int64_t dim, int64_t max_q_len,
                                       int dtype, void* stream) {
-  (void)n_queries; (void)n_documents;
+  return maxsim_packed_forward_with_argmax_ordered(
+      queries, query_offsets, documents, document_offsets, pair_query_ids, pair_document_ids,
+      nullptr, scores, argmax, n_pairs, n_queries, n_documents, total_q_tokens, total_d_tokens,
+      dim, max_q_len, dtype, stream);
+}
+
+int maxsim_packed_backward_grouped(const float* dscore, const void* queries,
+                                   const int32_t* query_offsets, const void* documents,
+                                   const int32_t* document_offsets,
+                                   const int32_t* pair_query_ids,
+                                   const int32_t* pair_document_ids,
+                                   const int32_t* order_by_query, const int32_t* ends_by_query,
+                                   const int32_t* order_by_document,
+                                   const int32_t* ends_by_document, const int32_t* argmax,
+                                   float* grad_queries, float* grad_documents, int64_t n_pairs,
+                                   int64_t n_queries, int64_t n_documents,
+                                   int64_t total_q_tokens, int64_t total_d_tokens, int64_t dim,
+                                   int64_t max_q_len, int dtype, void* stream) {
   if (!fits_i32(dim) || !fits_i32(max_q_len) || !fits_i32(total_q_tokens) || !fits_i32(total_d_tokens))
     return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
-  if (max_q_len <= 0) return fail(MAXSIM_EINVAL, "max_q_len must be > 0; got %lld", (long long)max_q_len);
+  if (n_queries < 0 || n_documents < 0) return fail(MAXSIM_EINVAL, "sizes must be positive");
   PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
                              pair_document_ids, n_pairs, dim, max_q_len, total_q_tokens,
                              total_d_tokens);
-  return run_forward<kPacked, true>(t, scores, argmax, dtype, stream);
+  if (order_by_query && ends_by_query && order_by_document && ends_by_document) {
+    t.order_q = order_by_query; t.ends_q = ends_by_query;
+    t.order_d = order_by_document; t.ends_d = ends_by_document;
+  }
+  return run_backward<kPacked>(t, dscore, argmax, grad_queries, grad_documents, total_q_tokens,
+                               total_d_tokens, 0, dtype, stream, n_queries, n_documents);
 }
 
 int maxsim_packed_backward(const float* dscore, const void* queries, const int32_t* query_offsets,
@@ -462,14 +560,11 @@ int maxsim_packed_backward(const float* dscore, const void* queries, const int32
                            int64_t n_pairs, int64_t n_queries, int64_t n_documents,
                            int64_t total_q_tokens, int64_t total_d_tokens, int64_t dim,
                            int64_t max_q_len, int dtype, void* stream) {
-  (void)n_queries; (void)n_documents;
-  if (!fits_i32(dim) || !fits_i32(max_q_len) || !fits_i32(total_q_tokens) || !fits_i32(total_d_tokens))
-    return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
-  PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
-                             pair_document_ids, n_pairs, dim, max_q_len, total_q_tokens,
-                             total_d_tokens);
-  return run_backward<kPacked>(t, dscore, argmax, grad_queries, grad_documents, total_q_tokens,
-                               total_d_tokens, 0, dtype, stream);
+  return maxsim_packed_backward_grouped(dscore, queries, query_offsets, documents, document_offsets,
+                                        pair_query_ids, pair_document_ids, nullptr, nullptr,
+                                        nullptr, nullptr, argmax, grad_queries, grad_documents,
+                                        n_pairs, n_queries, n_documents, total_q_tokens,
+                                        total_d_tokens, dim, max_q_len, dtype, stream);
 }
 
 int maxsim_padded_forward(const void* queries, const int32_t* query_lengths, const void* documents,

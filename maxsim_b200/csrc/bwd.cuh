@@ -11,8 +11,11 @@
 //   * grad_d of the contrastive layout inverts the argmax per document in
 //     shared memory (counting sort of the entries by winning token) and then
 //     gathers, one owner warp per document token, one store per row;
-//   * packed pair grids, whose pair list is arbitrary, use vector reductions
-//     (red.global.add) after a zero fill.
+//   * packed pair grids, whose pair list is arbitrary: when the caller
+//     supplies the list grouped by query and by document (group.cuh), grad_q
+//     is the same gather over a query's group and grad_d has one owner warp
+//     per document that zero-fills its rows and adds its group's routed rows;
+//     otherwise vector reductions (red.global.add) after a zero fill.
 #pragma once
 
 #include "common.cuh"
@@ -283,6 +286,156 @@ bwd_dd_padded_kernel(PairTable t, const float* __restrict__ dscore,
 }
 
 // ---------------------------------------------------------------------------
+// Packed pair lists with groups (t.order_q / ends_q / order_d / ends_d set).
+// Needs dim % 8 == 0 and 16-byte aligned bases.  Both kernels write every
+// output row exactly once: no zero fill, no atomics, same sums on every run up
+// to the order of a group's members.
+// ---------------------------------------------------------------------------
+
+// grad_q: one warp per (query, token slot).  Each half-warp fetches one pair's
+// winning document row with 128-bit loads; four rows in flight per lane.
+template <typename T>
+__global__ void __launch_bounds__(kBwdWarps * 32)
+bwd_dq_packed_kernel(PairTable t, const float* __restrict__ dscore,
+                     const int32_t* __restrict__ argmax, float* __restrict__ dq,
+                     int64_t n_queries) {
+  const int lane = threadIdx.x & 31, half = lane >> 4, hl = lane & 15;
+  const int dim = t.dim, slots = t.q_slots;
+  const int64_t row = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
+  if (row >= n_queries * slots) return;
+  const int64_t b = row / slots;
+  const int i = (int)(row - b * slots);
+  const int q0 = __ldg(t.ia + b);
+  const int Lq = min(__ldg(t.ia + b + 1) - q0, slots);
+  if (i >= Lq) return;
+  const int beg = b ? __ldg(t.ends_q + b - 1) : 0;
+  const int C = __ldg(t.ends_q + b) - beg;
+  const T* D = reinterpret_cast<const T*>(t.documents);
+
+  for (int kb = 0; kb < dim; kb += 128) {
+    const int k = kb + hl * 8;
+    const bool k_ok = k < dim;
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int c0 = 0; c0 < C; c0 += 32) {
+      const int c = c0 + lane;
+      float gl = 0.f;
+      int32_t src = -1;  // winning document row of the group's member c0+lane, or -1
+      if (c < C) {
+        const int64_t p = __ldg(t.order_q + beg + c);
+        const int j = __ldg(argmax + p * slots + i);
+        const int di = __ldg(t.id + p);
+        const int d0 = __ldg(t.ib + di);
+        const int Ld = __ldg(t.ib + di + 1) - d0;
+        if (j >= 0 && j < Ld) {
+          src = d0 + j;
+          gl = __ldg(dscore + p);
+        }
+      }
+      const int n = min(32, C - c0);
+      for (int l0 = 0; l0 < n; l0 += 8) {
+        Row8<T> rows[4];
+        float gw[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int l = (l0 + 2 * u + half) & 31;
+          const float gv = __shfl_sync(0xffffffffu, gl, l);
+          const int32_t sr = __shfl_sync(0xffffffffu, src, l);
+          const bool ok = (l0 + 2 * u + half < n) && sr >= 0 && k_ok;
+          gw[u] = ok ? gv : 0.f;
+          rows[u].zero();
+          if (ok) rows[u].load(D + (int64_t)sr * dim + k);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) rows[u].fma_into(gw[u], acc);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
+    if (half == 0 && k_ok) {
+      float4* out = reinterpret_cast<float4*>(dq + ((int64_t)q0 + i) * dim + k);
+      out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    }
+  }
+}
+
+// grad_d: one warp per document.  The warp zero-fills the document's rows,
+// then walks the document's group: for every pair, the winning token of each
+// query token receives g * q_i.  Lane l owns dims [4l, 4l+4) (+128 m) of every
+// row, so the read-modify-write of a row is private to a lane and needs no
+// atomics; query rows of four tokens are fetched ahead of their updates.
+template <typename T>
+__global__ void __launch_bounds__(kBwdWarps * 32)
+bwd_dd_packed_kernel(PairTable t, const float* __restrict__ dscore,
+                     const int32_t* __restrict__ argmax, float* __restrict__ dd,
+                     int64_t n_documents) {
+  const int lane = threadIdx.x & 31;
+  const int dim = t.dim, slots = t.q_slots;
+  const int64_t b = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
+  if (b >= n_documents) return;
+  const int d0 = __ldg(t.ib + b);
+  const int Ld = max(0, __ldg(t.ib + b + 1) - d0);
+  float* base = dd + (int64_t)d0 * dim;
+  {
+    float4* z = reinterpret_cast<float4*>(base);
+    const int64_t n4 = (int64_t)Ld * dim / 4;
+    for (int64_t e = lane; e < n4; e += 32) z[e] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  __syncwarp();
+  const int beg = b ? __ldg(t.ends_d + b - 1) : 0;
+  const int C = __ldg(t.ends_d + b) - beg;
+  const T* Q = reinterpret_cast<const T*>(t.queries);
+  const bool vec = true;
+  for (int c = 0; c < C; ++c) {
+    const int64_t p = __ldg(t.order_d + beg + c);
+    const float gv = __ldg(dscore + p);
+    const int qi = __ldg(t.ic + p);
+    const int q0 = __ldg(t.ia + qi);
+    const int Lq = min(__ldg(t.ia + qi + 1) - q0, slots);
+    for (int i0 = 0; i0 < Lq; i0 += 32) {
+      int jl = -1;
+      if (i0 + lane < Lq) {
+        jl = __ldg(argmax + p * slots + i0 + lane);
+        if (jl < 0 || jl >= Ld) jl = -1;
+      }
+      const int n = min(32, Lq - i0);
+      for (int u0 = 0; u0 < n; u0 += 4) {
+        int j[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) j[u] = __shfl_sync(0xffffffffu, jl, (u0 + u) & 31);
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (u0 + u >= n) j[u] = -1;
+        for (int k = lane * 4; k < dim; k += 128) {
+          float qv[4][4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (j[u] >= 0) {
+              load4<T>(Q + ((int64_t)q0 + i0 + u0 + u) * dim, vec, k, dim, qv[u]);
+            } else {
+              qv[u][0] = qv[u][1] = qv[u][2] = qv[u][3] = 0.f;
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (j[u] < 0) continue;
+            float4* dst = reinterpret_cast<float4*>(base + (int64_t)j[u] * dim + k);
+            float4 cur = *dst;
+            cur.x = fmaf(gv, qv[u][0], cur.x);
+            cur.y = fmaf(gv, qv[u][1], cur.y);
+            cur.z = fmaf(gv, qv[u][2], cur.z);
+            cur.w = fmaf(gv, qv[u][3], cur.w);
+            *dst = cur;
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Atomic routing (any layout).  One warp per pair.  Outputs must be zeroed.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
@@ -297,8 +450,9 @@ bwd_route_atomic_kernel(PairTable t, const float* __restrict__ dscore,
                         const int32_t* __restrict__ argmax, float* __restrict__ dq,
                         float* __restrict__ dd, int vec_ok) {
   const int lane = threadIdx.x & 31;
-  const int64_t p = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
-  if (p >= t.n_pairs) return;
+  const int64_t pos = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
+  if (pos >= t.n_pairs) return;
+  const int64_t p = pair_at<LAYOUT>(t, pos);
   const int dim = t.dim, slots = t.q_slots;
   const PairGeom g = pair_geom<LAYOUT>(t, p);
   const float gv = __ldg(dscore + p);

@@ -28,6 +28,17 @@ struct PairTable {
   const int32_t* ib;
   const int32_t* ic;
   const int32_t* id;
+  // packed only, may be null: processing order.  Position k of the grid works on
+  // pair order[k] (a permutation of [0, n_pairs) that puts pairs of the same
+  // document next to each other, see group.cuh); results still land in the
+  // pair's own slot.
+  const int32_t* order;
+  // packed backward only, may be null: the pair list grouped by query and by
+  // document.  Group b of a grouping is order_x[(b ? ends_x[b-1] : 0) .. ends_x[b]).
+  const int32_t* order_q;
+  const int32_t* ends_q;
+  const int32_t* order_d;
+  const int32_t* ends_d;
   int64_t n_pairs;
   int64_t q_rows;    // total query token rows
   int64_t d_rows;    // total document token rows
@@ -43,6 +54,15 @@ struct PairGeom {
   int32_t Lq;
   int32_t Ld;
 };
+
+// Pair worked on at grid position `pos`.
+template <int LAYOUT>
+__device__ __forceinline__ int64_t pair_at(const PairTable& t, int64_t pos) {
+  if constexpr (LAYOUT == kPacked) {
+    if (t.order) return (int64_t)__ldg(t.order + pos);
+  }
+  return pos;
+}
 
 template <int LAYOUT>
 __device__ __forceinline__ PairGeom pair_geom(const PairTable& t, int64_t p) {

@@ -123,13 +123,16 @@ struct __align__(16) TileMetaB {
 
 struct Geo32 {
   int32_t q_row0, d_row0, Lq, Ld;
+  int32_t pair;  // the pair these rows belong to (differs from the grid position under an order)
 };
 
 // Pair geometry with 32-bit rows (the dispatcher guarantees every row index
 // and pair index fits).
 template <int LAYOUT>
-__device__ __forceinline__ Geo32 geo32(const PairTable& t, int32_t p) {
+__device__ __forceinline__ Geo32 geo32(const PairTable& t, int32_t pos) {
   Geo32 g;
+  const int32_t p = (int32_t)pair_at<LAYOUT>(t, pos);
+  g.pair = p;
   if constexpr (LAYOUT == kPadded) {
     const int32_t b = (int32_t)((uint32_t)p / (uint32_t)t.C);
     g.q_row0 = b * t.q_slots;
@@ -188,37 +191,44 @@ fwd_mma_kernel(PairTable t, float* __restrict__ scores, int32_t* __restrict__ ar
   const uint32_t ring_u32 = smem_u32(ring);
   const uint32_t bars_u32 = smem_u32(bars);
 
+  __shared__ int s_next_chunk;  // chunks of this CTA handed out so far
+  if (threadIdx.x == 0) s_next_chunk = 0;
   if (lane == 0) {
     for (int s = 0; s < kStages; ++s) mbar_init(bars_u32 + 8 * s, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
-  __syncwarp();
+  __syncthreads();
 
   // ---- feeding cursor (uniform across the warp) ---------------------------
-  // Chunks of `pairs_per_chunk` consecutive pairs are dealt round-robin:
-  // consecutive chunks go to different SMs first, then to different warps.
+  // Chunks of `pairs_per_chunk` consecutive pairs are dealt round-robin over
+  // the CTAs (CTA b owns chunks b, b + grid, b + 2*grid, ...); inside a CTA the
+  // warps take the CTA's chunks from a shared counter as they become free, so
+  // ragged documents do not leave some warps idle while others still work.
   const int32_t n_pairs = (int32_t)t.n_pairs;
   const int32_t n_chunks = (n_pairs + pairs_per_chunk - 1) / pairs_per_chunk;
-  const int32_t warps_total = (int32_t)gridDim.x * kMmaWarps;
-  int32_t f_chunk = warp * (int32_t)gridDim.x + (int32_t)blockIdx.x;  // chunk of the NEXT pair
   int32_t fp = -1;     // pair being fed (-1: none left)
   int32_t np = -1;     // the pair after it, geometry already requested
   int32_t np_end = 0;  // end of np's chunk
   Geo32 cur, nxt;
-  cur.q_row0 = cur.d_row0 = cur.Lq = cur.Ld = 0;
+  cur.q_row0 = cur.d_row0 = cur.Lq = cur.Ld = cur.pair = 0;
   nxt = cur;
   int f_q0 = 0, f_j0 = 0;
 
   auto fetch_next = [&]() {  // np <- successor of np within this warp's chunks; request its geometry
     if (np >= 0 && np + 1 < np_end) {
       ++np;
-    } else if (f_chunk < n_chunks) {
-      np = f_chunk * pairs_per_chunk;
-      np_end = min(np + pairs_per_chunk, n_pairs);
-      f_chunk += warps_total;
     } else {
-      np = -1;
+      int k = 0;
+      if (lane == 0) k = atomicAdd(&s_next_chunk, 1);
+      k = __shfl_sync(0xffffffffu, k, 0);
+      const int64_t chunk = (int64_t)k * gridDim.x + blockIdx.x;
+      if (chunk < n_chunks) {
+        np = (int32_t)chunk * pairs_per_chunk;
+        np_end = min(np + pairs_per_chunk, n_pairs);
+      } else {
+        np = -1;
+      }
     }
     if (np >= 0) nxt = geo32<LAYOUT>(t, np);
   };
@@ -241,7 +251,7 @@ fwd_mma_kernel(PairTable t, float* __restrict__ scores, int32_t* __restrict__ ar
     const int n_valid = max(0, min(kTileTokens, cur.Ld - f_j0));
     if (lane == 0) {
       TileMetaA a;
-      a.pair = fp;
+      a.pair = cur.pair;
       a.j0 = f_j0;
       a.Ld = cur.Ld;
       a.lq_q0 = cur.Lq | (f_q0 << 16);

@@ -52,7 +52,8 @@ fwd_simt_kernel(PairTable t, float* __restrict__ scores, int32_t* __restrict__ a
   int* red_i = reinterpret_cast<int*>(red_v + 4 * kSimtRows);  // [4][32]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
-  for (int64_t p = blockIdx.x; p < t.n_pairs; p += gridDim.x) {
+  for (int64_t pos = blockIdx.x; pos < t.n_pairs; pos += gridDim.x) {
+    const int64_t p = pair_at<LAYOUT>(t, pos);
     const PairGeom g = pair_geom<LAYOUT>(t, p);
     const T* Q = reinterpret_cast<const T*>(t.queries) + g.q_row0 * dim;
     const T* D = reinterpret_cast<const T*>(t.documents) + g.d_row0 * dim;
