@@ -532,6 +532,37 @@ def run_contrastive_profile(args):
                       "doc_tokens": int(d.shape[0]), "ms_per_step": statistics.median(ms)}), flush=True)
 
 
+def run_packed_profile(args):
+    """A few train steps (forward+argmax, backward) of the packed pair grid,
+    nothing else: the command a profiler wraps."""
+    import maxsim_b200 as maxsim
+    from maxsim_b200 import workloads as W
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    maxsim._ops.set_pair_grouping(not args.list_order)
+    wl = W.c4_packed_grid_fp16()
+    q = W.to_torch(wl.queries, "fp16", dev).requires_grad_(True)
+    d = W.to_torch(wl.documents, "fp16", dev).requires_grad_(True)
+    qo = torch.from_numpy(wl.query_offsets).to(dev)
+    do = torch.from_numpy(wl.document_offsets).to(dev)
+    pq = torch.from_numpy(wl.pair_query_ids).to(dev)
+    pd = torch.from_numpy(wl.pair_document_ids).to(dev)
+    g = torch.from_numpy(wl.dscore).to(dev)
+
+    def step():
+        q.grad = None
+        d.grad = None
+        maxsim.score_pairs_packed_train(q, qo, d, do, pq, pd, max_q_len=32).backward(g)
+
+    for _ in range(max(1, args.warmup)):
+        step()
+    ms = _event_ms(step, max(1, args.steps))
+    print(json.dumps({"profile_run": True, "workload": "c4_packed_grid_fp16",
+                      "pairs": int(pq.shape[0]), "order": "list" if args.list_order else "grouped",
+                      "ms_per_step": statistics.median(ms)}), flush=True)
+
+
 def run_gpu_arm(args):
     import maxsim_b200 as maxsim
     from maxsim_b200 import _ops
@@ -747,11 +778,17 @@ def main():
     ap.add_argument("--profile-contrastive", action="store_true",
                     help="run only contrastive forward+backward steps of the ties configuration "
                          "(Nq=Nb=1024, or 512 with --small); for profiler captures")
+    ap.add_argument("--profile-packed", action="store_true",
+                    help="run only train steps of the packed pair grid (65536 pairs); for profiler captures")
+    ap.add_argument("--list-order", action="store_true",
+                    help="with --profile-packed: visit pairs in list order, atomic backward")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
     elif args.profile_contrastive:
         run_contrastive_profile(args)
+    elif args.profile_packed:
+        run_packed_profile(args)
     else:
         run_gpu_arm(args)
 

@@ -361,77 +361,134 @@ bwd_dq_packed_kernel(PairTable t, const float* __restrict__ dscore,
   }
 }
 
-// grad_d: one warp per document.  The warp zero-fills the document's rows,
-// then walks the document's group: for every pair, the winning token of each
-// query token receives g * q_i.  Lane l owns dims [4l, 4l+4) (+128 m) of every
-// row, so the read-modify-write of a row is private to a lane and needs no
-// atomics; query rows of four tokens are fetched ahead of their updates.
+// grad_d: one warp per document.  The warp walks the document's group: for
+// every pair, the winning token of each query token receives g * q_i.  A bitmap
+// in shared memory records which rows were written: the first contribution to
+// a row is a plain store, later ones read-modify-write it, and rows that got
+// none are zero-filled at the end -- so most rows are written exactly once and
+// there is no window between a zero-fill pass and the updates in which the
+// lines could leave L2.  Lane l owns dims [4l, 4l+4) (+128 m) of every row, so
+// an update is private to a lane and needs no atomics; the query rows of four
+// tokens are fetched ahead of their updates.
+constexpr int kDdPassRows = 1024;  // rows covered by one pass of the bitmap
+
 template <typename T>
 __global__ void __launch_bounds__(kBwdWarps * 32)
 bwd_dd_packed_kernel(PairTable t, const float* __restrict__ dscore,
                      const int32_t* __restrict__ argmax, float* __restrict__ dd,
                      int64_t n_documents) {
-  const int lane = threadIdx.x & 31;
+  __shared__ uint32_t s_written[kBwdWarps][kDdPassRows / 32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int dim = t.dim, slots = t.q_slots;
-  const int64_t b = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
+  const int64_t b = (int64_t)blockIdx.x * kBwdWarps + warp;
   if (b >= n_documents) return;
   const int d0 = __ldg(t.ib + b);
   const int Ld = max(0, __ldg(t.ib + b + 1) - d0);
-  float* base = dd + (int64_t)d0 * dim;
-  {
-    float4* z = reinterpret_cast<float4*>(base);
-    const int64_t n4 = (int64_t)Ld * dim / 4;
-    for (int64_t e = lane; e < n4; e += 32) z[e] = make_float4(0.f, 0.f, 0.f, 0.f);
-  }
-  __syncwarp();
   const int beg = b ? __ldg(t.ends_d + b - 1) : 0;
   const int C = __ldg(t.ends_d + b) - beg;
   const T* Q = reinterpret_cast<const T*>(t.queries);
+  uint32_t* written = s_written[warp];
   const bool vec = true;
-  for (int c = 0; c < C; ++c) {
-    const int64_t p = __ldg(t.order_d + beg + c);
-    const float gv = __ldg(dscore + p);
-    const int qi = __ldg(t.ic + p);
-    const int q0 = __ldg(t.ia + qi);
-    const int Lq = min(__ldg(t.ia + qi + 1) - q0, slots);
-    for (int i0 = 0; i0 < Lq; i0 += 32) {
-      int jl = -1;
-      if (i0 + lane < Lq) {
-        jl = __ldg(argmax + p * slots + i0 + lane);
-        if (jl < 0 || jl >= Ld) jl = -1;
+
+  for (int row0 = 0; row0 < Ld; row0 += kDdPassRows) {
+    const int nrows = min(kDdPassRows, Ld - row0);
+    float* base = dd + ((int64_t)d0 + row0) * dim;
+    written[lane] = 0u;
+    __syncwarp();
+    int32_t m_p = 0, m_q0 = 0, m_Lq = 0;
+    float m_g = 0.f;
+    for (int c = 0; c < C; ++c) {
+      // lane l fetches the geometry of the group's member c + l: one chain of
+      // dependent loads per 32 pairs instead of one per pair
+      if ((c & 31) == 0) {
+        m_p = 0; m_g = 0.f; m_q0 = 0; m_Lq = 0;
+        if (c + lane < C) {
+          m_p = __ldg(t.order_d + beg + c + lane);
+          m_g = __ldg(dscore + m_p);
+          const int qi = __ldg(t.ic + m_p);
+          m_q0 = __ldg(t.ia + qi);
+          m_Lq = min(__ldg(t.ia + qi + 1) - m_q0, slots);
+        }
       }
-      const int n = min(32, Lq - i0);
-      for (int u0 = 0; u0 < n; u0 += 4) {
-        int j[4];
+      const int64_t p = __shfl_sync(0xffffffffu, m_p, c & 31);
+      const float gv = __shfl_sync(0xffffffffu, m_g, c & 31);
+      const int q0 = __shfl_sync(0xffffffffu, m_q0, c & 31);
+      const int Lq = __shfl_sync(0xffffffffu, m_Lq, c & 31);
+      for (int i0 = 0; i0 < Lq; i0 += 32) {
+        int jl = -1;
+        if (i0 + lane < Lq) {
+          jl = __ldg(argmax + p * slots + i0 + lane) - row0;
+          if (jl < 0 || jl >= nrows || jl + row0 >= Ld) jl = -1;
+        }
+        const int n = min(32, Lq - i0);
+        for (int u0 = 0; u0 < n; u0 += 4) {
+          int j[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) j[u] = __shfl_sync(0xffffffffu, jl, (u0 + u) & 31);
+          for (int u = 0; u < 4; ++u) j[u] = __shfl_sync(0xffffffffu, jl, (u0 + u) & 31);
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (u0 + u >= n) j[u] = -1;
-        for (int k = lane * 4; k < dim; k += 128) {
-          float qv[4][4];
+          for (int u = 0; u < 4; ++u)
+            if (u0 + u >= n) j[u] = -1;
+          if (j[0] < 0 && j[1] < 0 && j[2] < 0 && j[3] < 0) continue;
+          // which of the four rows have been written before (by an earlier
+          // batch, or by an earlier token of this batch)
+          bool fresh[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
+            fresh[u] = false;
             if (j[u] >= 0) {
-              load4<T>(Q + ((int64_t)q0 + i0 + u0 + u) * dim, vec, k, dim, qv[u]);
-            } else {
-              qv[u][0] = qv[u][1] = qv[u][2] = qv[u][3] = 0.f;
+              fresh[u] = ((written[j[u] >> 5] >> (j[u] & 31)) & 1u) == 0u;
+#pragma unroll
+              for (int v = 0; v < u; ++v)
+                if (j[v] == j[u]) fresh[u] = false;
             }
           }
+          __syncwarp();
+          if (lane == 0) {
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (j[u] < 0) continue;
-            float4* dst = reinterpret_cast<float4*>(base + (int64_t)j[u] * dim + k);
-            float4 cur = *dst;
-            cur.x = fmaf(gv, qv[u][0], cur.x);
-            cur.y = fmaf(gv, qv[u][1], cur.y);
-            cur.z = fmaf(gv, qv[u][2], cur.z);
-            cur.w = fmaf(gv, qv[u][3], cur.w);
-            *dst = cur;
+            for (int u = 0; u < 4; ++u)
+              if (j[u] >= 0) written[j[u] >> 5] |= 1u << (j[u] & 31);
+          }
+          __syncwarp();
+          for (int k = lane * 4; k < dim; k += 128) {
+            float qv[4][4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (j[u] >= 0) {
+                load4<T>(Q + ((int64_t)q0 + i0 + u0 + u) * dim, vec, k, dim, qv[u]);
+              } else {
+                qv[u][0] = qv[u][1] = qv[u][2] = qv[u][3] = 0.f;
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              if (j[u] < 0) continue;
+              float4* dst = reinterpret_cast<float4*>(base + (int64_t)j[u] * dim + k);
+              float4 cur = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (!fresh[u]) cur = *dst;
+              cur.x = fmaf(gv, qv[u][0], cur.x);
+              cur.y = fmaf(gv, qv[u][1], cur.y);
+              cur.z = fmaf(gv, qv[u][2], cur.z);
+              cur.w = fmaf(gv, qv[u][3], cur.w);
+              *dst = cur;
+            }
           }
         }
       }
     }
+    __syncwarp();
+    // rows nobody routed to
+    for (int r0 = 0; r0 < nrows; r0 += 32) {
+      const uint32_t word = written[r0 >> 5];
+      uint32_t missing = ~word;
+      if (nrows - r0 < 32) missing &= (1u << (nrows - r0)) - 1u;
+      while (missing) {
+        const int r = r0 + __ffs(missing) - 1;
+        missing &= missing - 1;
+        for (int k = lane * 4; k < dim; k += 128)
+          *reinterpret_cast<float4*>(base + (int64_t)r * dim + k) = make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    __syncwarp();
   }
 }
 
