@@ -218,6 +218,27 @@ MAXSIM_API int maxsim_packed_backward_grouped(
     int64_t total_q_tokens, int64_t total_d_tokens,
     int64_t dim, int64_t max_q_len, int dtype, void* stream);
 
+/* group_pairs for callers that cannot allocate device memory (no counterpart
+ * in the reference).  Same result in `order` as maxsim_b200_group_pairs, but
+ * the n_bins counters live in a 4 MB array inside the library (one per GPU
+ * that loads it, held until the process exits) instead of caller memory, and
+ * the call performs no allocation of any kind.  It is meant for hosts that
+ * bind this ABI without a device allocator of their own (a C, Go or Rust
+ * service with fixed buffers), for processes that gave all device memory to
+ * one pool at start-up, where a later cudaMalloc fails or fragments the pool,
+ * and for latency-critical loops that must not run into the device-wide
+ * synchronisation cudaMalloc and cudaFree imply.  Limits and rules:
+ *  - n_bins <= 1048576 (MAXSIM_EUNSUPPORTED beyond, with a message);
+ *  - the first call on a device looks up the array's device address; make it
+ *    before any stream capture begins on that device;
+ *  - every call uses the same array (it is cleared at the start of each call):
+ *    two calls that overlap on the GPU, from different streams or threads,
+ *    race on it -- issue them on one stream or serialise them yourself;
+ *  - the group ends are not returned; the order feeds the *_ordered forward
+ *    operators. */
+MAXSIM_API int maxsim_b200_group_pairs_static(const int32_t* ids, int64_t n_pairs,
+                                              int64_t n_bins, int32_t* order, void* stream);
+
 /* ------------------------------------------------------------------------
  * Padded candidates.
  * queries [B*Lq_max, dim], query_lengths [B],

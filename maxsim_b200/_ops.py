@@ -47,6 +47,7 @@ _SIGNATURES = {
     "maxsim_b200_unpack_rows": (c_int, [_P] * 3 + [_I64] * 4 + [_P]),
     "maxsim_b200_topk_rows": (c_int, [_P] + [_I64] * 3 + [_P] * 3),
     "maxsim_b200_group_pairs": (c_int, [_P, _I64, _I64, _P, _P, _P]),
+    "maxsim_b200_group_pairs_static": (c_int, [_P, _I64, _I64, _P, _P]),
     "maxsim_forward_ordered": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_forward_with_argmax_ordered": (c_int, [_P] * 9 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_backward_grouped": (c_int, [_P] * 14 + [_I64] * 7 + [c_int, _P]),

@@ -468,6 +468,53 @@ int maxsim_b200_group_pairs(const int32_t* pair_document_ids, int64_t n_pairs,
   return launch_check("group_scatter_kernel");
 }
 
+// Counters of maxsim_b200_group_pairs_static.  In host code the array's name is
+// only a handle: its device address comes from cudaGetSymbolAddress, looked up
+// once per device with that device current.
+constexpr int64_t kStaticGroupBins = 1 << 20;
+static __device__ __align__(256) int32_t g_static_group_bins[kStaticGroupBins];
+
+static int static_group_bins(int32_t** out) {
+  static std::atomic<int32_t*> cached[kMaxDevices];
+  int dev = 0;
+  MAXSIM_CUDA(cudaGetDevice(&dev));
+  const bool track = dev >= 0 && dev < kMaxDevices;
+  int32_t* p = track ? cached[dev].load(std::memory_order_acquire) : nullptr;
+  if (!p) {
+    MAXSIM_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_static_group_bins));
+    if (track) cached[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return MAXSIM_OK;
+}
+
+int maxsim_b200_group_pairs_static(const int32_t* ids, int64_t n_pairs, int64_t n_bins,
+                                   int32_t* order, void* stream) {
+  if (n_pairs < 0 || n_bins <= 0 || !fits_i32(n_pairs))
+    return fail(MAXSIM_EINVAL, "n_pairs must be >= 0 and within int32, n_bins > 0");
+  if (n_bins > kStaticGroupBins)
+    return fail(MAXSIM_EUNSUPPORTED,
+                "n_bins=%lld exceeds the %lld ids the built-in scratch array holds; use "
+                "maxsim_b200_group_pairs with caller-provided memory",
+                (long long)n_bins, (long long)kStaticGroupBins);
+  if (n_pairs == 0) return MAXSIM_OK;
+  if (!ids || !order) return fail(MAXSIM_EINVAL, "null pointer argument");
+  int32_t* bins = nullptr;
+  if (int rc = static_group_bins(&bins)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MAXSIM_CUDA(cudaMemsetAsync(bins, 0, (size_t)n_bins * sizeof(int32_t), st));
+  int64_t grid = (n_pairs + kGroupThreads - 1) / kGroupThreads;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  if (grid > cap) grid = cap;
+  group_count_kernel<<<(unsigned)grid, kGroupThreads, 0, st>>>(ids, n_pairs, (int32_t)n_bins, bins);
+  if (int rc = launch_check("group_count_kernel")) return rc;
+  group_scan_kernel<<<1, kGroupScanThreads, 0, st>>>(bins, (int32_t)n_bins);
+  if (int rc = launch_check("group_scan_kernel")) return rc;
+  group_scatter_kernel<<<(unsigned)grid, kGroupThreads, 0, st>>>(ids, n_pairs, (int32_t)n_bins, bins,
+                                                                 order);
+  return launch_check("group_scatter_kernel");
+}
+
 int maxsim_forward_ordered(const void* queries, const int32_t* query_offsets,
                            const void* documents, const int32_t* document_offsets,
                            const int32_t* pair_query_ids, const int32_t* pair_document_ids,
