@@ -121,6 +121,16 @@ MAXSIM_API int maxsim_b200_pack_rows(const void* padded, const int32_t* offsets,
 MAXSIM_API int maxsim_b200_unpack_rows(const void* packed, const int32_t* offsets, void* padded,
                                        int64_t n_segments, int64_t L_max, int64_t row_bytes,
                                        int64_t packed_rows, void* stream);
+/* copy_valid_rows: both tensors are padded [n_segments, L_max, row]; segment
+ * n's first lengths[n] rows (lengths on the device) are copied from src to
+ * dst, padding rows of dst are left as they are.  src may be device memory or
+ * page-locked host memory (its host pointer; the library asks the driver for
+ * the device-side mapping and fails with MAXSIM_EINVAL if there is none), in
+ * which case the kernel reads it over PCIe and padding never crosses the bus. */
+MAXSIM_API int maxsim_b200_copy_valid_rows(const void* src, int src_is_host,
+                                           const int32_t* lengths, void* dst,
+                                           int64_t n_segments, int64_t L_max,
+                                           int64_t row_bytes, void* stream);
 MAXSIM_API int maxsim_b200_topk_rows(const float* scores, int64_t rows, int64_t cols, int64_t k,
                                      float* values, int64_t* indices, void* stream);
 

@@ -27,7 +27,8 @@ import torch
 
 from . import _validate as _v
 from ._ops import ops
-from .layout import pack_padded, rerank_order, rerank_topk, unpack_packed
+from .layout import (pack_padded, rerank_order, rerank_topk, score_candidates_padded_from_host,
+                     unpack_packed)
 
 __all__ = [
     "score_pairs_packed", "score_pairs_packed_with_argmax", "score_pairs_packed_train",
@@ -38,6 +39,7 @@ __all__ = [
     "score_packed", "score_packed_with_argmax", "score_packed_train",
     "lengths_from_prefix_mask", "contrastive_loss",
     "pack_padded", "unpack_packed", "rerank_topk", "rerank_order",
+    "score_candidates_padded_from_host",
 ]
 
 __version__ = "0.1.0"

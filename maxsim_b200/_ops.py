@@ -46,6 +46,7 @@ _SIGNATURES = {
     "maxsim_b200_pack_rows": (c_int, [_P] * 3 + [_I64] * 4 + [_P]),
     "maxsim_b200_unpack_rows": (c_int, [_P] * 3 + [_I64] * 4 + [_P]),
     "maxsim_b200_topk_rows": (c_int, [_P] + [_I64] * 3 + [_P] * 3),
+    "maxsim_b200_copy_valid_rows": (c_int, [_P, c_int, _P, _P] + [_I64] * 3 + [_P]),
     "maxsim_b200_group_pairs": (c_int, [_P, _I64, _I64, _P, _P, _P]),
     "maxsim_b200_group_pairs_static": (c_int, [_P, _I64, _I64, _P, _P]),
     "maxsim_forward_ordered": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
@@ -202,6 +203,34 @@ def unpack_rows(packed: torch.Tensor, offsets: torch.Tensor, L_max: int) -> torc
             _stream_ptr())
     _check(rc, "maxsim_b200_unpack_rows")
     return padded
+
+
+def copy_valid_rows(src: torch.Tensor, lengths: torch.Tensor, dst: torch.Tensor) -> torch.Tensor:
+    """Copy the first ``lengths[n]`` rows of every segment of padded ``src
+    [N, L_max, ...]`` into ``dst`` (same shape and dtype, on a CUDA device);
+    padding rows of ``dst`` keep their contents.  ``src`` may be on the same
+    device or in pinned host memory, which the kernel then reads over PCIe."""
+    dev = _require_cuda(dst, lengths)
+    if src.shape != dst.shape or src.dtype != dst.dtype:
+        raise RuntimeError("src and dst must have the same shape and dtype")
+    if not src.is_contiguous() or not dst.is_contiguous():
+        raise RuntimeError("src and dst must be contiguous")
+    host = src.device.type == "cpu"
+    if host and not src.is_pinned():
+        raise RuntimeError("a host source must be in pinned (page-locked) memory")
+    if not host and src.device != dev:
+        raise RuntimeError(f"all inputs must share a device; got {dev} and {src.device}")
+    ln = _i32(lengths.reshape(-1))
+    n, L = src.shape[0], src.shape[1]
+    if ln.shape[0] != n:
+        raise RuntimeError("lengths must have one entry per segment")
+    row_bytes = (src[0, 0].numel() if n and L else 1) * src.element_size()
+    with torch.cuda.device(dev):
+        rc = load_library().maxsim_b200_copy_valid_rows(
+            src.data_ptr(), 1 if host else 0, _ptr(ln), dst.data_ptr(), n, L, row_bytes,
+            _stream_ptr())
+    _check(rc, "maxsim_b200_copy_valid_rows")
+    return dst
 
 
 def topk_rows(scores: torch.Tensor, k: int):

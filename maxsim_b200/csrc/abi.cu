@@ -425,6 +425,53 @@ int maxsim_b200_unpack_rows(const void* packed, const int32_t* offsets, void* pa
                                  stream);
 }
 
+int maxsim_b200_copy_valid_rows(const void* src, int src_is_host, const int32_t* lengths,
+                                void* dst, int64_t n_segments, int64_t L_max, int64_t row_bytes,
+                                void* stream) {
+  if (n_segments < 0 || L_max < 0 || row_bytes <= 0 || !fits_i32(L_max))
+    return fail(MAXSIM_EINVAL, "sizes must be >= 0 (row_bytes > 0) and L_max must fit int32");
+  if (n_segments == 0 || L_max == 0) return MAXSIM_OK;
+  if (!src || !dst || !lengths) return fail(MAXSIM_EINVAL, "null pointer argument");
+  const void* dsrc = src;
+  if (src_is_host) {
+    void* mapped = nullptr;
+    cudaError_t e = cudaHostGetDevicePointer(&mapped, const_cast<void*>(src), 0);
+    if (e != cudaSuccess || !mapped) {
+      (void)cudaGetLastError();
+      return fail(MAXSIM_EINVAL,
+                  "source is not page-locked host memory mapped for this device (%s)",
+                  cudaGetErrorString(e));
+    }
+    dsrc = mapped;
+  }
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int sms = sm_count();
+  const int64_t slab_bytes = L_max * row_bytes;
+  // one CTA per segment at a time unless the segments are few and long
+  int64_t gy = 1;
+  if (n_segments < 2 * sms) {
+    gy = (slab_bytes + 16 * 8 * kCopyThreads - 1) / (16 * 8 * kCopyThreads);
+    gy = gy < 1 ? 1 : (gy > 16 ? 16 : gy);
+  }
+  int64_t gx = n_segments;
+  const int64_t cap = (int64_t)sms * 32;
+  if (gx * gy > cap) gx = cap / gy;
+  dim3 grid((unsigned)gx, (unsigned)gy);
+  const bool a16 = aligned16(dsrc) && aligned16(dst) && row_bytes % 16 == 0;
+  const bool a4 = ((reinterpret_cast<uintptr_t>(dsrc) | reinterpret_cast<uintptr_t>(dst)) & 3u) == 0 &&
+                  row_bytes % 4 == 0;
+  if (a16)
+    valid_rows_copy_kernel<uint4><<<grid, kCopyThreads, 0, st>>>(dsrc, dst, lengths, n_segments,
+                                                                 (int)L_max, row_bytes);
+  else if (a4)
+    valid_rows_copy_kernel<uint32_t><<<grid, kCopyThreads, 0, st>>>(dsrc, dst, lengths, n_segments,
+                                                                    (int)L_max, row_bytes);
+  else
+    valid_rows_copy_kernel<uint8_t><<<grid, kCopyThreads, 0, st>>>(dsrc, dst, lengths, n_segments,
+                                                                   (int)L_max, row_bytes);
+  return launch_check("valid_rows_copy_kernel");
+}
+
 int maxsim_b200_topk_rows(const float* scores, int64_t rows, int64_t cols, int64_t k,
                           float* values, int64_t* indices, void* stream) {
   if (rows < 0 || cols < 0 || k < 0 || k > cols) return fail(MAXSIM_EINVAL, "need 0 <= k <= cols");

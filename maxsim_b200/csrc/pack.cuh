@@ -118,6 +118,39 @@ segment_copy_kernel(const void* __restrict__ src, void* __restrict__ dst,
   }
 }
 
+// Valid-row copy between two padded tensors of the same shape: segment n's
+// first lengths[n] rows go from src to dst, the padding rows are not touched.
+// Made for sources in pinned host memory (the kernel reads it over PCIe through
+// the device mapping of the allocation): a padded rerank batch is about one
+// third padding, which a plain host-to-device copy would move as well.  Eight
+// independent 16-byte loads are in flight per thread before the first store.
+template <typename V>
+__global__ void __launch_bounds__(kCopyThreads)
+valid_rows_copy_kernel(const void* __restrict__ src, void* __restrict__ dst,
+                       const int32_t* __restrict__ lengths, long long n_seg, int L_max,
+                       long long row_bytes) {
+  const long long slab = (long long)L_max * row_bytes / (long long)sizeof(V);
+  const long long rowv = row_bytes / (long long)sizeof(V);
+  const long long start = (long long)blockIdx.y * kCopyThreads + threadIdx.x;
+  const long long step = (long long)gridDim.y * kCopyThreads;
+  for (long long n = blockIdx.x; n < n_seg; n += gridDim.x) {
+    int len = __ldg(lengths + n);
+    len = len < 0 ? 0 : (len > L_max ? L_max : len);
+    const long long valid = (long long)len * rowv;
+    const V* s = reinterpret_cast<const V*>(src) + n * slab;
+    V* d = reinterpret_cast<V*>(dst) + n * slab;
+    long long i = start;
+    for (; i + 7 * step < valid; i += 8 * step) {
+      V v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = s[i + u * step];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) d[i + u * step] = v[u];
+    }
+    for (; i < valid; i += step) d[i] = s[i];
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Ranking.  One CTA sorts one score row in shared memory (bitonic network over
 // 64-bit keys) and writes the best k entries, best first.  Key = order-

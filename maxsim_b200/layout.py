@@ -12,7 +12,11 @@ host, and rank with ``scores.argsort(dim=1, descending=True)``
 * :func:`unpack_packed` -- packed rows back to ``[N, L_max, D]`` with zero
   padding; differentiable;
 * :func:`rerank_topk` -- the ``k`` best candidates of every row of a score
-  matrix, best first, equal scores by ascending candidate index.
+  matrix, best first, equal scores by ascending candidate index;
+* :func:`score_candidates_padded_from_host` -- rerank a padded batch that
+  lives in pinned host memory: a kernel reads only the valid token rows over
+  PCIe (a padded batch is about one third padding), the scores go back to the
+  host.
 """
 
 from __future__ import annotations
@@ -22,8 +26,10 @@ from typing import Optional, Tuple
 import torch
 
 from . import _ops
+from . import _validate as _v
 
-__all__ = ["pack_padded", "unpack_packed", "rerank_topk", "rerank_order"]
+__all__ = ["pack_padded", "unpack_packed", "rerank_topk", "rerank_order",
+           "score_candidates_padded_from_host"]
 
 _eager = torch.compiler.disable
 
@@ -132,3 +138,67 @@ def rerank_order(scores: torch.Tensor) -> torch.Tensor:
     """Full ranking: what ``scores.argsort(dim=1, descending=True)`` gives,
     with ties by ascending index."""
     return rerank_topk(scores, scores.shape[1])[1]
+
+
+_STAGING = {}
+
+
+def _staging_for(documents: torch.Tensor, device: torch.device) -> torch.Tensor:
+    key = (tuple(documents.shape), documents.dtype, str(device))
+    buf = _STAGING.get(key)
+    if buf is None:
+        _STAGING.clear()  # one batch shape at a time: these buffers are large
+        buf = torch.empty(documents.shape, dtype=documents.dtype, device=device)
+        _STAGING[key] = buf
+    return buf
+
+
+@_eager
+def score_candidates_padded_from_host(queries: torch.Tensor, documents: torch.Tensor,
+                                      query_lengths: torch.Tensor, doc_lengths: torch.Tensor, *,
+                                      device, staging: Optional[torch.Tensor] = None,
+                                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """:func:`maxsim_b200.score_candidates_padded` for a batch in host memory.
+
+    ``queries [B, Lq, D]``, ``documents [B, C, Ld, D]`` and the two length
+    tensors are CPU tensors.  When ``documents`` is pinned, a kernel on
+    ``device`` reads each candidate's first ``doc_lengths[b, c]`` rows straight
+    from it, so padding rows never cross PCIe; a pageable ``documents`` is
+    copied whole.  ``staging`` is the device-side ``[B, C, Ld, D]`` landing
+    buffer (one is kept per batch shape when not given; its padding rows hold
+    whatever they held before, and no kernel reads them).
+
+    Returns the ``[B, C]`` fp32 scores on the host.  With a pinned ``out`` the
+    copy back is asynchronous on the current stream of ``device`` and ``out``
+    is returned: synchronise that stream (or the device) before reading it.
+    """
+    for name, t in (("queries", queries), ("documents", documents),
+                    ("query_lengths", query_lengths), ("doc_lengths", doc_lengths)):
+        if t.device.type != "cpu":
+            raise RuntimeError(f"{name} must be a CPU tensor; got device {t.device}")
+    B, C, Lq, Ld, D = _v.check_padded(queries, documents, query_lengths, doc_lengths)
+    device = torch.device(device)
+    if device.type != "cuda":
+        raise RuntimeError(f"device must be a CUDA device (maxsim_b200 has no CPU path); got {device}")
+    documents = documents.contiguous()
+    with torch.cuda.device(device):
+        q = queries.contiguous().to(device, non_blocking=True)
+        qlen = query_lengths.contiguous().to(device, non_blocking=True).to(torch.int32)
+        dlen = doc_lengths.contiguous().to(device, non_blocking=True).to(torch.int32)
+        if staging is None:
+            staging = _staging_for(documents, device)
+        elif (staging.shape != documents.shape or staging.dtype != documents.dtype
+              or staging.device != device or not staging.is_contiguous()):
+            raise ValueError("staging must be a contiguous tensor on `device` shaped and typed like documents")
+        if documents.is_pinned():
+            _ops.copy_valid_rows(documents.view(B * C, Ld, D), dlen.view(-1), staging.view(B * C, Ld, D))
+        else:
+            staging.copy_(documents)
+        scores = _ops.ops.maxsim_padded_forward(q.view(B * Lq, D), qlen, staging.view(B * C * Ld, D),
+                                                dlen.view(-1), int(Lq), int(Ld), int(C)).view(B, C)
+        if out is not None:
+            if tuple(out.shape) != (B, C) or out.dtype != torch.float32 or out.device.type != "cpu":
+                raise ValueError(f"out must be a CPU float32 tensor of shape [B={B}, C={C}]")
+            out.copy_(scores, non_blocking=True)
+            return out
+        return scores.cpu()

@@ -206,3 +206,58 @@ def test_full_size_pack_round_trip():
     assert torch.equal(back[mask], enc[mask])
     assert bool((back[~mask] == 0).all())
     assert torch.equal(docs, enc[mask])
+
+
+def test_copy_valid_rows_from_pinned_host_and_from_device():
+    torch.manual_seed(2)
+    N, L, D = 37, 50, 128
+    src = torch.randn(N, L, D).to(torch.float16)
+    lengths = torch.randint(1, L + 1, (N,), dtype=torch.int32)
+    mask = (torch.arange(L)[None, :] < lengths[:, None])
+    for source in (src.pin_memory(), src.to(DEV)):
+        dst = torch.full((N, L, D), 7.0, dtype=torch.float16, device=DEV)
+        _ops.copy_valid_rows(source, lengths.to(DEV), dst)
+        got = dst.cpu()
+        assert torch.equal(got[mask], src[mask])
+        assert bool((got[~mask] == 7.0).all())          # padding rows untouched
+    with pytest.raises(RuntimeError, match="pinned"):
+        _ops.copy_valid_rows(src, lengths.to(DEV), torch.empty_like(src, device=DEV))
+
+
+@pytest.mark.parametrize("pinned", [True, False])
+def test_rerank_from_host_equals_the_device_path(pinned):
+    from maxsim_b200 import workloads as W
+    wl = W.c3_large_rerank_fp16(seed=12, Nq=6, C=40, Ld=300)
+    q = W.to_torch(wl.queries, "fp16")
+    d = W.to_torch(wl.documents, "fp16")
+    # padding rows hold values that would change the scores if they were read
+    pad = torch.arange(300)[None, None, :] >= torch.from_numpy(wl.doc_lengths)[:, :, None]
+    d[pad] = 1.0e4
+    ql, dl = torch.from_numpy(wl.query_lengths), torch.from_numpy(wl.doc_lengths)
+    want = maxsim.score_candidates_padded(q.to(DEV), d.to(DEV), ql.to(DEV), dl.to(DEV)).cpu()
+    if pinned:
+        q, d = q.pin_memory(), d.pin_memory()
+    got = maxsim.score_candidates_padded_from_host(q, d, ql, dl, device=DEV)
+    assert got.device.type == "cpu" and got.dtype == torch.float32
+    assert torch.equal(got, want)
+    out = torch.empty(6, 40, dtype=torch.float32).pin_memory()
+    staging = torch.full(d.shape, float("nan"), dtype=torch.float16, device=DEV)
+    ret = maxsim.score_candidates_padded_from_host(q, d, ql, dl, device=DEV, staging=staging, out=out)
+    torch.cuda.synchronize()
+    assert ret is out and torch.equal(out, want)
+    ws, _ = oracle.score_candidates_padded(q.float().numpy(), d.float().numpy(),
+                                           wl.query_lengths, wl.doc_lengths)
+    np.testing.assert_allclose(got.numpy(), ws, rtol=2e-2, atol=1e-2)
+
+
+def test_rerank_from_host_rejects_device_tensors_and_bad_staging():
+    q = torch.zeros(2, 32, 128, dtype=torch.float16)
+    d = torch.zeros(2, 3, 40, 128, dtype=torch.float16)
+    ql, dl = torch.tensor([32, 32]), torch.full((2, 3), 40)
+    with pytest.raises(RuntimeError, match="CPU tensor"):
+        maxsim.score_candidates_padded_from_host(q.to(DEV), d, ql, dl, device=DEV)
+    with pytest.raises(ValueError, match="staging"):
+        maxsim.score_candidates_padded_from_host(q, d, ql, dl, device=DEV,
+                                                 staging=torch.empty(1, device=DEV))
+    with pytest.raises(ValueError, match="doc_lengths"):
+        maxsim.score_candidates_padded_from_host(q, d, ql, dl * 0, device=DEV)
