@@ -363,13 +363,14 @@ bwd_dq_packed_kernel(PairTable t, const float* __restrict__ dscore,
 
 // grad_d: one warp per document.  The warp walks the document's group: for
 // every pair, the winning token of each query token receives g * q_i.  A bitmap
-// in shared memory records which rows were written: the first contribution to
-// a row is a plain store, later ones read-modify-write it, and rows that got
-// none are zero-filled at the end -- so most rows are written exactly once and
-// there is no window between a zero-fill pass and the updates in which the
-// lines could leave L2.  Lane l owns dims [4l, 4l+4) (+128 m) of every row, so
-// an update is private to a lane and needs no atomics; the query rows of four
-// tokens are fetched ahead of their updates.
+// (lane w keeps the word of rows 32w .. 32w+31) records which rows were
+// written: the first contribution to a row is a plain store, later ones
+// read-modify-write it, and rows that got none are zero-filled at the end --
+// so most rows are written exactly once and there is no window between a
+// zero-fill pass and the updates in which the lines could leave L2.  Lane l
+// owns dims [4l, 4l+4) (+128 m) of every row, so an update is private to a
+// lane and needs no atomics; the query rows of four tokens are fetched ahead
+// of their updates.
 constexpr int kDdPassRows = 1024;  // rows covered by one pass of the bitmap
 
 template <typename T>
@@ -377,24 +378,21 @@ __global__ void __launch_bounds__(kBwdWarps * 32)
 bwd_dd_packed_kernel(PairTable t, const float* __restrict__ dscore,
                      const int32_t* __restrict__ argmax, float* __restrict__ dd,
                      int64_t n_documents) {
-  __shared__ uint32_t s_written[kBwdWarps][kDdPassRows / 32];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
   const int dim = t.dim, slots = t.q_slots;
-  const int64_t b = (int64_t)blockIdx.x * kBwdWarps + warp;
+  const int64_t b = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
   if (b >= n_documents) return;
   const int d0 = __ldg(t.ib + b);
   const int Ld = max(0, __ldg(t.ib + b + 1) - d0);
   const int beg = b ? __ldg(t.ends_d + b - 1) : 0;
   const int C = __ldg(t.ends_d + b) - beg;
   const T* Q = reinterpret_cast<const T*>(t.queries);
-  uint32_t* written = s_written[warp];
-  const bool vec = true;
+  const int dim4 = dim >> 2;
 
   for (int row0 = 0; row0 < Ld; row0 += kDdPassRows) {
     const int nrows = min(kDdPassRows, Ld - row0);
-    float* base = dd + ((int64_t)d0 + row0) * dim;
-    written[lane] = 0u;
-    __syncwarp();
+    float4* base4 = reinterpret_cast<float4*>(dd + ((int64_t)d0 + row0) * dim);
+    uint32_t written = 0u;  // this lane's word of the bitmap
     int32_t m_p = 0, m_q0 = 0, m_Lq = 0;
     float m_g = 0.f;
     for (int c = 0; c < C; ++c) {
@@ -418,77 +416,57 @@ bwd_dd_packed_kernel(PairTable t, const float* __restrict__ dscore,
         int jl = -1;
         if (i0 + lane < Lq) {
           jl = __ldg(argmax + p * slots + i0 + lane) - row0;
-          if (jl < 0 || jl >= nrows || jl + row0 >= Ld) jl = -1;
+          if (jl < 0 || jl >= nrows) jl = -1;
         }
         const int n = min(32, Lq - i0);
-        for (int u0 = 0; u0 < n; u0 += 4) {
-          int j[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) j[u] = __shfl_sync(0xffffffffu, jl, (u0 + u) & 31);
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (u0 + u >= n) j[u] = -1;
-          if (j[0] < 0 && j[1] < 0 && j[2] < 0 && j[3] < 0) continue;
-          // which of the four rows have been written before (by an earlier
-          // batch, or by an earlier token of this batch)
-          bool fresh[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            fresh[u] = false;
-            if (j[u] >= 0) {
-              fresh[u] = ((written[j[u] >> 5] >> (j[u] & 31)) & 1u) == 0u;
-#pragma unroll
-              for (int v = 0; v < u; ++v)
-                if (j[v] == j[u]) fresh[u] = false;
-            }
-          }
-          __syncwarp();
-          if (lane == 0) {
-#pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (j[u] >= 0) written[j[u] >> 5] |= 1u << (j[u] & 31);
-          }
-          __syncwarp();
-          for (int k = lane * 4; k < dim; k += 128) {
+        const T* qrow = Q + ((int64_t)q0 + i0) * dim;
+        for (int kb = 0; kb < dim; kb += 128) {
+          const int k = kb + lane * 4;
+          const bool k_ok = k < dim;
+          uint32_t seen = written;  // rows written before this (pair, i0) block
+          for (int u0 = 0; u0 < n; u0 += 4) {
+            int j[4];
             float qv[4][4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              if (j[u] >= 0) {
-                load4<T>(Q + ((int64_t)q0 + i0 + u0 + u) * dim, vec, k, dim, qv[u]);
-              } else {
-                qv[u][0] = qv[u][1] = qv[u][2] = qv[u][3] = 0.f;
-              }
+              j[u] = __shfl_sync(0xffffffffu, jl, (u0 + u) & 31);
+              if (u0 + u >= n) j[u] = -1;
+              qv[u][0] = qv[u][1] = qv[u][2] = qv[u][3] = 0.f;
+              if (j[u] >= 0 && k_ok) load4<T>(qrow + (u0 + u) * dim, true, k, dim, qv[u]);
             }
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              if (j[u] < 0) continue;
-              float4* dst = reinterpret_cast<float4*>(base + (int64_t)j[u] * dim + k);
-              float4 cur = make_float4(0.f, 0.f, 0.f, 0.f);
-              if (!fresh[u]) cur = *dst;
-              cur.x = fmaf(gv, qv[u][0], cur.x);
-              cur.y = fmaf(gv, qv[u][1], cur.y);
-              cur.z = fmaf(gv, qv[u][2], cur.z);
-              cur.w = fmaf(gv, qv[u][3], cur.w);
-              *dst = cur;
+              if (j[u] < 0) continue;  // uniform: j comes from a shuffle
+              const uint32_t word = __shfl_sync(0xffffffffu, seen, j[u] >> 5);
+              const bool fresh = ((word >> (j[u] & 31)) & 1u) == 0u;
+              if (lane == (j[u] >> 5)) seen |= 1u << (j[u] & 31);
+              if (k_ok) {
+                float4* dst = base4 + j[u] * dim4 + (k >> 2);
+                float4 cur = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (!fresh) cur = *dst;
+                cur.x = fmaf(gv, qv[u][0], cur.x);
+                cur.y = fmaf(gv, qv[u][1], cur.y);
+                cur.z = fmaf(gv, qv[u][2], cur.z);
+                cur.w = fmaf(gv, qv[u][3], cur.w);
+                *dst = cur;
+              }
             }
           }
+          if (kb + 128 >= dim) written = seen;  // every 128-wide block replays the same rows
         }
       }
     }
-    __syncwarp();
     // rows nobody routed to
-    for (int r0 = 0; r0 < nrows; r0 += 32) {
-      const uint32_t word = written[r0 >> 5];
-      uint32_t missing = ~word;
-      if (nrows - r0 < 32) missing &= (1u << (nrows - r0)) - 1u;
+    for (int w = 0; w * 32 < nrows; ++w) {
+      uint32_t missing = ~__shfl_sync(0xffffffffu, written, w);
+      if (nrows - w * 32 < 32) missing &= (1u << (nrows - w * 32)) - 1u;
       while (missing) {
-        const int r = r0 + __ffs(missing) - 1;
+        const int r = w * 32 + __ffs(missing) - 1;
         missing &= missing - 1;
         for (int k = lane * 4; k < dim; k += 128)
-          *reinterpret_cast<float4*>(base + (int64_t)r * dim + k) = make_float4(0.f, 0.f, 0.f, 0.f);
+          base4[r * dim4 + (k >> 2)] = make_float4(0.f, 0.f, 0.f, 0.f);
       }
     }
-    __syncwarp();
   }
 }
 

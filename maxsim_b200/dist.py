@@ -110,17 +110,21 @@ def _gather_shards(documents: torch.Tensor, lengths: torch.Tensor, group, world:
     indices of the real (non-filler) documents, the number of columns, the
     per-rank ``(tokens, documents)`` sizes and ``t_pad``."""
     dev = documents.device
+    nccl = dist.get_backend(group) == "nccl"
     meta = torch.tensor([documents.shape[0], lengths.numel()], dtype=torch.int64, device=dev)
-    metas = [torch.zeros_like(meta) for _ in range(world)]
-    dist.all_gather(metas, meta, group=group)
-    sizes = [(int(m[0].item()), int(m[1].item())) for m in metas]
+    metas = torch.empty((world, 2), dtype=torch.int64, device=dev)
+    if nccl:
+        dist.all_gather_into_tensor(metas, meta, group=group)
+    else:
+        dist.all_gather(list(metas.unbind(0)), meta, group=group)
+    sizes = [(int(t), int(n)) for t, n in metas.tolist()]  # one transfer for all ranks
     t_pad = max(s[0] for s in sizes) + 1
     n_max = max(s[1] for s in sizes)
 
     doc_pad = documents.new_zeros((t_pad, documents.shape[1]))
     doc_pad[: documents.shape[0]] = documents
     doc_parts = torch.empty((world * t_pad, documents.shape[1]), dtype=documents.dtype, device=dev)
-    if dist.get_backend(group) == "nccl":
+    if nccl:
         handle = dist.all_gather_into_tensor(doc_parts, doc_pad, group=group, async_op=True)
     else:
         handle = dist.all_gather(list(doc_parts.view(world, t_pad, -1).unbind(0)), doc_pad,
@@ -128,8 +132,12 @@ def _gather_shards(documents: torch.Tensor, lengths: torch.Tensor, group, world:
 
     len_pad = torch.zeros(n_max, dtype=torch.int32, device=dev)
     len_pad[: lengths.numel()] = lengths.to(torch.int32)
-    len_parts = [torch.empty_like(len_pad) for _ in range(world)]
-    dist.all_gather(len_parts, len_pad, group=group)
+    len_all = torch.empty((world, n_max), dtype=torch.int32, device=dev)
+    if nccl:
+        dist.all_gather_into_tensor(len_all, len_pad, group=group)
+    else:
+        dist.all_gather(list(len_all.unbind(0)), len_pad, group=group)
+    len_parts = len_all.unbind(0)
 
     # combined document list: real documents of rank r, then its filler.  The
     # column indices of the real documents are built on the host (the sizes are
