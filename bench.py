@@ -462,6 +462,83 @@ def bench_train_steps(dev, peaks, full: bool):
     return out
 
 
+# The reference's own benchmark matrix (scripts/bench_matrix.py:711-724 of the
+# reference: shapes; :237-265: method -- one CUDA-event pair per iteration with
+# a synchronise after it, median of 30 after 10 warm-ups, the Python wrapper
+# and, for the training rows, two input clones inside the timed call).  The
+# published figures are the reference's maxsim_step_ms on an H200
+# (bench_results/v2/h200.json), i.e. other hardware.
+REFERENCE_MATRIX = [
+    ("Contrastive", "contrastive", dict(Nq=32, Nb=32, Lq=32, Ld=80, dim=128), {"fp16": 0.261, "bf16": 0.272}),
+    ("LongDocs", "contrastive", dict(Nq=32, Nb=32, Lq=32, Ld=512, dim=128), {"fp16": 0.270}),
+    ("BigBatch", "contrastive", dict(Nq=64, Nb=64, Lq=32, Ld=128, dim=128), {"fp16": 0.320, "bf16": 0.321}),
+    ("Rerank", "padded", dict(B=32, C=50, Lq=32, Ld=180, dim=128), {"fp16": 0.327, "bf16": 0.338}),
+    ("HeavyRerank", "padded", dict(B=32, C=100, Lq=32, Ld=256, dim=128), {"fp16": 0.335, "bf16": 0.374}),
+    ("PackedRerank", "packed", dict(B=32, C=50, Lq=32, Ld=180, dim=128), {"fp16": 5.527}),
+    ("PackedHeavyRerank", "packed", dict(B=32, C=100, Lq=32, Ld=256, dim=128), {"fp16": 14.640}),
+]
+
+
+def bench_reference_matrix(dev):
+    import maxsim_b200 as maxsim
+
+    def timed(fn, iters=30, warm=10):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        out = []
+        for _ in range(iters):
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            out.append(a.elapsed_time(b))
+        return statistics.median(out)
+
+    rows = []
+    for name, kind, shp, published in REFERENCE_MATRIX:
+        for dname, ref_ms in published.items():
+            dtype = torch.float16 if dname == "fp16" else torch.bfloat16
+            gen = torch.Generator().manual_seed(1234)
+            if kind == "contrastive":
+                q = torch.randn(shp["Nq"], shp["Lq"], shp["dim"], generator=gen).to(dev, dtype)
+                docs = torch.randn(shp["Nb"] * shp["Ld"], shp["dim"], generator=gen).to(dev, dtype)
+                cu = torch.arange(0, (shp["Nb"] + 1) * shp["Ld"], shp["Ld"], dtype=torch.int32, device=dev)
+
+                def step():
+                    q_r = q.detach().clone().requires_grad_(True)
+                    d_r = docs.detach().clone().requires_grad_(True)
+                    maxsim.score_contrastive_train(q_r, d_r, cu).sum().backward()
+            else:
+                B, C, Lq, Ld, dim = (shp[k] for k in ("B", "C", "Lq", "Ld", "dim"))
+                q = torch.randn(B, Lq, dim, generator=gen).to(dev, dtype)
+                d = torch.randn(B, C, Ld, dim, generator=gen).to(dev, dtype)
+                qlen = torch.full((B,), Lq, dtype=torch.int32, device=dev)
+                dlen = torch.full((B, C), Ld, dtype=torch.int32, device=dev)
+                if kind == "padded":
+                    def step():
+                        return maxsim.score_candidates_padded(q, d, qlen, dlen)
+                else:
+                    qf = q.reshape(B * Lq, dim).contiguous()
+                    df = d.reshape(B * C * Ld, dim).contiguous()
+                    qoff = torch.arange(0, (B + 1) * Lq, Lq, dtype=torch.int32, device=dev)
+                    doff = torch.arange(0, (B * C + 1) * Ld, Ld, dtype=torch.int32, device=dev)
+                    qids = torch.arange(B, dtype=torch.int32, device=dev).repeat_interleave(C)
+                    dids = torch.arange(B * C, dtype=torch.int32, device=dev)
+
+                    def step():
+                        return maxsim.score_pairs_packed(qf, qoff, df, doff, qids, dids, max_q_len=Lq)
+            ms = timed(step)
+            rows.append({"name": name, "dtype": dname, "shape": shp, "ms": round(ms, 4),
+                         "reference_h200_ms": ref_ms, "ratio": round(ref_ms / ms, 2)})
+    return {"rows": rows,
+            "note": "the reference's benchmark matrix with its timing method (per-iteration CUDA events "
+                    "and synchronise, median of 30, Python wrapper and input clones included); "
+                    "reference_h200_ms are the reference's published H200 figures (other hardware), "
+                    "ratio = reference_h200_ms / ms"}
+
+
 def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
     """Contrastive training step of the 1024 x 1024 ties configuration with
     queries and documents sharded over the ranks: all-gather of the document
@@ -721,10 +798,12 @@ def run_gpu_arm(args):
 
     train = None
     cpu_base = None
+    ref_matrix = None
     del documents, d_flat, data
     torch.cuda.empty_cache()
     if world == 1:
         train = bench_train_steps(dev, peaks, full=not args.small)
+        ref_matrix = bench_reference_matrix(dev)
         v, cores, sample = cpu_padded_baseline(target_seconds=2.0 if args.small else 12.0)
         cpu_base = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
     else:
@@ -767,6 +846,8 @@ def run_gpu_arm(args):
             line["cpu_baseline"] = cpu_base
         if train is not None:
             line["train_step"] = train
+        if ref_matrix is not None:
+            line["reference_matrix"] = ref_matrix
         print(json.dumps(line), flush=True)
     if dist:
         dist.barrier()

@@ -119,7 +119,7 @@ def layout_stats(items) -> list:
     dev = next(t for pair in items for t in pair if t is not None).device
     out = torch.empty((len(items), 8), dtype=torch.int64, device=dev)
     keep = []
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         for row, (offsets, ids) in enumerate(items):
             ref = offsets if offsets is not None else ids
             o = offsets.detach().reshape(-1).contiguous() if offsets is not None else None
@@ -146,7 +146,7 @@ def contrastive_ce(scores: torch.Tensor, targets: torch.Tensor, temperature: flo
         raise RuntimeError("scores must be [Nq, Nb] and targets [Nq]")
     loss_rows = torch.empty((s.shape[0],), dtype=torch.float32, device=dev)
     dscore = torch.empty_like(s) if want_grad else None
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_b200_contrastive_ce(
             _ptr(s), _ptr(t), _ptr(loss_rows), _ptr(dscore) if dscore is not None else 0,
             s.shape[0], s.shape[1], float(temperature), float(grad_scale), _stream_ptr())
@@ -161,7 +161,7 @@ def offsets_from_lengths(lengths: torch.Tensor, L_max: int):
     ln = _i32(lengths.reshape(-1))
     offsets = torch.empty((ln.shape[0] + 1,), dtype=torch.int32, device=dev)
     total = torch.empty((1,), dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_b200_offsets_from_lengths(
             _ptr(ln), ln.shape[0], int(L_max), offsets.data_ptr(), total.data_ptr(), _stream_ptr())
     _check(rc, "maxsim_b200_offsets_from_lengths")
@@ -177,7 +177,7 @@ def pack_rows(padded: torch.Tensor, offsets: torch.Tensor, packed_rows: int) -> 
     n, L = src.shape[0], src.shape[1]
     packed = torch.empty((int(packed_rows),) + tuple(src.shape[2:]), dtype=src.dtype, device=dev)
     row_bytes = (src[0, 0].numel() if n and L else 1) * src.element_size()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_b200_pack_rows(
             _ptr(src), _ptr(off), _ptr(packed), n, L, row_bytes, int(packed_rows), _stream_ptr())
     _check(rc, "maxsim_b200_pack_rows")
@@ -197,7 +197,7 @@ def unpack_rows(packed: torch.Tensor, offsets: torch.Tensor, L_max: int) -> torc
     row_bytes *= src.element_size()
     if row_bytes == 0:
         return padded
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_b200_unpack_rows(
             _ptr(src), _ptr(off), _ptr(padded), n, int(L_max), row_bytes, src.shape[0],
             _stream_ptr())
@@ -225,7 +225,7 @@ def copy_valid_rows(src: torch.Tensor, lengths: torch.Tensor, dst: torch.Tensor)
     if ln.shape[0] != n:
         raise RuntimeError("lengths must have one entry per segment")
     row_bytes = (src[0, 0].numel() if n and L else 1) * src.element_size()
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_b200_copy_valid_rows(
             src.data_ptr(), 1 if host else 0, _ptr(ln), dst.data_ptr(), n, L, row_bytes,
             _stream_ptr())
@@ -239,15 +239,52 @@ def topk_rows(scores: torch.Tensor, k: int):
     s = scores.contiguous().to(torch.float32)
     values = torch.empty((s.shape[0], int(k)), dtype=torch.float32, device=dev)
     indices = torch.empty((s.shape[0], int(k)), dtype=torch.int64, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_b200_topk_rows(
             _ptr(s), s.shape[0], s.shape[1], int(k), _ptr(values), _ptr(indices), _stream_ptr())
     _check(rc, "maxsim_b200_topk_rows")
     return values, indices
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_exchange_device = getattr(torch.cuda, "_exchange_device", None)
+
+
 def _stream_ptr() -> int:
+    """Handle of the current stream of the current device.  The raw query is
+    about ten times cheaper than building a ``torch.cuda.Stream`` object,
+    which matters for the small launch-bound shapes."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+class _on_device:
+    """``with _on_device(dev):`` makes ``dev`` current for the library call,
+    like ``torch.cuda.device`` but without its argument parsing."""
+
+    __slots__ = ("idx", "prev")
+
+    def __init__(self, dev: torch.device):
+        self.idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        if _exchange_device is not None:
+            self.prev = _exchange_device(self.idx)
+        else:
+            self.prev = torch.cuda.current_device()
+            if self.prev != self.idx:
+                torch.cuda.set_device(self.idx)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev != self.idx and self.prev >= 0:
+            if _exchange_device is not None:
+                _exchange_device(self.prev)
+            else:
+                torch.cuda.set_device(self.prev)
+        return False
 
 
 def _ptr(t: torch.Tensor) -> int:
@@ -315,7 +352,7 @@ def group_pairs(ids: torch.Tensor, n_bins: int):
     flat = _i32(ids.reshape(-1))
     order = torch.empty((flat.shape[0],), dtype=torch.int32, device=dev)
     ends = torch.empty((max(int(n_bins), 1),), dtype=torch.int32, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_b200_group_pairs(
             _ptr(flat), flat.shape[0], max(int(n_bins), 1), ends.data_ptr(), _ptr(order),
             _stream_ptr())
@@ -374,7 +411,7 @@ def maxsim_forward(queries, query_offsets, documents, document_offsets,
         max_q_len = int((qoff[1:] - qoff[:-1]).max().item())
     if max_q_len <= 0:
         raise RuntimeError(f"max_q_len must be > 0; got {max_q_len}")
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         # score-only calls use the document order only if it is already known
         by_doc = _groups(pair_document_ids, pd, doff.shape[0] - 1, build=False)
         rc = load_library().maxsim_forward_ordered(
@@ -401,7 +438,7 @@ def maxsim_packed_forward_with_argmax(queries, query_offsets, documents, documen
     argmax = torch.empty((n_pairs, max_q_len), dtype=torch.int32, device=dev)
     if n_pairs == 0:
         return scores, argmax
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         by_doc = _groups(pair_document_ids, pd, doff.shape[0] - 1)
         rc = load_library().maxsim_packed_forward_with_argmax_ordered(
             _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd),
@@ -429,7 +466,7 @@ def maxsim_packed_backward(dscore, queries, query_offsets, documents, document_o
         raise RuntimeError("argmax must have shape [num_pairs, max_q_len]")
     dq = torch.empty(q.shape, dtype=torch.float32, device=dev)
     dd = torch.empty(d.shape, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         by_doc = _groups(pair_document_ids, pd, doff.shape[0] - 1)
         by_query = _groups(pair_query_ids, pq, qoff.shape[0] - 1)
         grouped = by_doc is not None and by_query is not None
@@ -481,7 +518,7 @@ def maxsim_padded_forward(queries, query_lengths, documents, doc_lengths,
     scores = torch.empty((B * C,), dtype=torch.float32, device=dev)
     if B * C == 0:
         return scores
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_padded_forward(
             _ptr(q), _ptr(qlen), _ptr(d), _ptr(dlen), _ptr(scores),
             B, C, Lq_max, Ld_max, q.shape[1], _code(q), _stream_ptr())
@@ -498,7 +535,7 @@ def maxsim_padded_forward_with_argmax(queries, query_lengths, documents, doc_len
     argmax = torch.empty((B * C, Lq_max), dtype=torch.int32, device=dev)
     if B * C == 0:
         return scores, argmax
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_padded_forward_with_argmax(
             _ptr(q), _ptr(qlen), _ptr(d), _ptr(dlen), _ptr(scores), _ptr(argmax),
             B, C, Lq_max, Ld_max, q.shape[1], _code(q), _stream_ptr())
@@ -519,7 +556,7 @@ def maxsim_padded_backward(dscore, queries, documents, query_lengths, doc_length
         raise RuntimeError("argmax must have shape [B * num_candidates, Lq_max]")
     dq = torch.empty(q.shape, dtype=torch.float32, device=dev)
     dd = torch.empty(d.shape, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_padded_backward(
             _ptr(g), _ptr(q), _ptr(d), _ptr(qlen), _ptr(dlen), _ptr(a), _ptr(dq), _ptr(dd),
             B, C, Lq_max, Ld_max, q.shape[1], _code(q), _stream_ptr())
@@ -561,7 +598,7 @@ def maxsim_contrastive_forward(queries, documents, document_offsets) -> torch.Te
     scores = torch.empty((Nq, Nb), dtype=torch.float32, device=dev)
     if Nq * Nb == 0:
         return scores
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_contrastive_forward(
             _ptr(q), _ptr(d), _ptr(off), _ptr(scores),
             Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
@@ -576,7 +613,7 @@ def maxsim_contrastive_forward_with_argmax(queries, documents, document_offsets)
     argmax = torch.empty((Nq, Nb, Lq), dtype=torch.int32, device=dev)
     if Nq * Nb == 0:
         return scores, argmax
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_contrastive_forward_with_argmax(
             _ptr(q), _ptr(d), _ptr(off), _ptr(scores), _ptr(argmax),
             Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
@@ -595,7 +632,7 @@ def maxsim_contrastive_backward(dscore, queries, documents, document_offsets, ar
         raise RuntimeError("argmax must have shape [Nq, Nb, Lq]")
     dq = torch.empty(q.shape, dtype=torch.float32, device=dev)
     dd = torch.empty(d.shape, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with _on_device(dev):
         rc = load_library().maxsim_contrastive_backward(
             _ptr(g), _ptr(q), _ptr(d), _ptr(off), _ptr(a), _ptr(dq), _ptr(dd),
             Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
