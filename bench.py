@@ -50,7 +50,7 @@ C3 = dict(Nq=256, Lq=32, C=1000, Ld=300, dim=128)
 # DRAM bytes per algorithmic byte for the streaming forward kernel, from the
 # ncu capture summarised in profiles/ (dram__bytes_read.sum + write.sum over the
 # algorithmic bytes of the captured launch).  None until a capture exists.
-NCU_TRAFFIC_RATIO = 1.0073  # (764.93 MB read + 5.53 MB written) / 764.87 MB; profiles/fwd_mma_kernel__c3_rerank_fp16.md
+NCU_TRAFFIC_RATIO = 1.0073  # (764.93 MB read + 5.53 MB written) / 764.87 MB, from the ncu capture of this kernel summarised under profiles/
 
 
 def _peaks():

@@ -134,4 +134,4 @@ def main(root: Path):
 
 
 if __name__ == "__main__":
-    main(Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    main(Path(sys.argv[1]) if len(sys.argv) > 1 else HERE.parents[2] / "reference")

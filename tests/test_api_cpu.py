@@ -183,13 +183,17 @@ def test_ops_namespace_matches_reference_operator_names():
 
 def test_reference_python_layer_runs_on_this_ops_namespace():
     """The reference's own maxsim/__init__.py imports and dispatches into this
-    package's operator namespace when it is installed as maxsim._ops (the seam
-    described in INTEGRATION.md).  Needs the reference checkout."""
+    package's operator namespace when it is installed as maxsim._ops, the one
+    seam through which the reference reaches its compiled kernels.  Needs a
+    checkout of the reference next to this repository (or in
+    $MAXSIM_REFERENCE_DIR); skipped without one."""
     import importlib
     import sys
     import types
 
-    ref = Path("/root/reference/torch-ext")
+    import os
+    ref = Path(os.environ.get("MAXSIM_REFERENCE_DIR",
+                              Path(__file__).resolve().parents[2] / "reference")) / "torch-ext"
     if not (ref / "maxsim" / "__init__.py").exists():
         pytest.skip("reference checkout not present")
     saved = {k: sys.modules.pop(k) for k in list(sys.modules) if k == "maxsim" or k.startswith("maxsim.")}
