@@ -431,8 +431,12 @@ def bench_train_steps(dev, peaks, full: bool):
             "ms_per_step": tpd, "pairs_per_s": 128 * 64 / (tpd * 1e-3),
             "step_hbm_frac": (valid + grad_bytes + 128 * 64 * 32 * 8) / (tpd * 1e-3) / (peaks["hbm_gbs"] * 1e9),
             "note": "B=128, C=64, Ld_max=300; step = forward+argmax, cross-entropy, backward through "
-                    "the public API; bytes = valid tokens + full-size fp32 grad_documents written "
-                    "once and cast to bf16 by autograd"}
+                    "the public API; gradients are written once by the kernels in bf16; step_hbm_frac "
+                    "still counts the bytes of the fp32-gradient-plus-cast formulation it replaces "
+                    "(valid tokens + 10 B per gradient element), step_hbm_frac_native the bytes that "
+                    "move now (valid tokens + 2 B per gradient element)",
+            "step_hbm_frac_native": (valid + dp.numel() * 2 + 128 * 64 * 32 * 8) / (tpd * 1e-3)
+            / (peaks["hbm_gbs"] * 1e9)}
         del qp, dp, wlp
 
         # either side of the operators: packing an encoder output, ranking a rerank result

@@ -319,6 +319,32 @@ MAXSIM_API int maxsim_contrastive_backward(
     int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim,
     int64_t total_d_tokens, int dtype, void* stream);
 
+/* Gradients in the inputs' element type (no compiled reference counterpart:
+ * the reference's operators return fp32 gradients, maxsim_cuda/maxsim.cu:
+ * 1180-1181, 1896-1897, and its Python layer lets autograd cast them to the
+ * leaf dtype, torch-ext/maxsim/__init__.py:771, 954).  Same arguments as
+ * maxsim_padded_backward / maxsim_contrastive_backward, but grad_queries and
+ * grad_documents are tensors of `dtype` (float16 or bfloat16): every gradient
+ * row is summed in fp32 registers and rounded once when it is stored, which is
+ * the value the cast of the fp32 result has, without the fp32 tensors and the
+ * cast's pass over them.  Only for shapes whose rows are stored exactly once
+ * (dim % 8 == 0, dim <= 128, 16-byte aligned tensors; padded: Lq_max <= 32,
+ * Ld_max <= 1024; contrastive: Nq * Lq <= 32768); otherwise the status is
+ * MAXSIM_EUNSUPPORTED, nothing is launched, and the caller uses the fp32
+ * operator. */
+MAXSIM_API int maxsim_padded_backward_native(
+    const float* dscore, const void* queries, const void* documents,
+    const int32_t* query_lengths, const int32_t* doc_lengths, const int32_t* argmax,
+    void* grad_queries, void* grad_documents,
+    int64_t B, int64_t C, int64_t Lq_max, int64_t Ld_max, int64_t dim,
+    int dtype, void* stream);
+MAXSIM_API int maxsim_contrastive_backward_native(
+    const float* dscore, const void* queries, const void* documents,
+    const int32_t* document_offsets, const int32_t* argmax,
+    void* grad_queries, void* grad_documents,
+    int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim, int64_t total_d_tokens,
+    int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

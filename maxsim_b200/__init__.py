@@ -25,6 +25,7 @@ from typing import Optional, Tuple
 
 import torch
 
+from . import _ops
 from . import _validate as _v
 from ._ops import ops
 from .layout import (pack_padded, rerank_order, rerank_topk, score_candidates_padded_from_host,
@@ -187,8 +188,13 @@ class _PaddedFn(torch.autograd.Function):
         B, C, Lq, Ld, D = ctx.shapes
         q, d, qlen, dlen, argmax = ctx.saved_tensors
         g = dscore.reshape(B * C).contiguous().to(torch.float32)
-        dq, dd = ops.maxsim_padded_backward(g, q, d, qlen, dlen, argmax,
-                                            int(Lq), int(Ld), int(C))
+        # 16-bit inputs: the kernels round each gradient row once on store, which is
+        # what autograd's cast of the fp32 result would give, without the extra pass
+        grads = _ops.padded_backward_native(g, q, d, qlen, dlen, argmax, int(Lq), int(Ld), int(C))
+        if grads is None:
+            grads = ops.maxsim_padded_backward(g, q, d, qlen, dlen, argmax,
+                                               int(Lq), int(Ld), int(C))
+        dq, dd = grads
         return dq.view(B, Lq, D), dd.view(B, C, Ld, D), None, None
 
 
@@ -239,8 +245,10 @@ class _ContrastiveFn(torch.autograd.Function):
     def backward(ctx, dscore):
         q, d, off, argmax = ctx.saved_tensors
         g = dscore.contiguous().to(torch.float32)
-        dq, dd = ops.maxsim_contrastive_backward(g, q, d, off, argmax)
-        return dq, dd, None
+        grads = _ops.contrastive_backward_native(g, q, d, off, argmax)
+        if grads is None:
+            grads = ops.maxsim_contrastive_backward(g, q, d, off, argmax)
+        return grads[0], grads[1], None
 
 
 @_eager
@@ -270,7 +278,6 @@ class _ContrastiveLossFn(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, queries, documents, document_offsets, targets, temperature):
-        from . import _ops
         q = queries.contiguous()
         d = documents.contiguous()
         off = document_offsets.to(dtype=torch.int32).contiguous()
@@ -284,8 +291,10 @@ class _ContrastiveLossFn(torch.autograd.Function):
     def backward(ctx, grad_out):
         q, d, off, argmax, dscore = ctx.saved_tensors
         g = dscore * grad_out.to(torch.float32)
-        dq, dd = ops.maxsim_contrastive_backward(g, q, d, off, argmax)
-        return dq, dd, None, None, None
+        grads = _ops.contrastive_backward_native(g, q, d, off, argmax)
+        if grads is None:
+            grads = ops.maxsim_contrastive_backward(g, q, d, off, argmax)
+        return grads[0], grads[1], None, None, None
 
 
 @_eager

@@ -61,6 +61,8 @@ _SIGNATURES = {
     "maxsim_contrastive_forward": (c_int, [_P] * 4 + [_I64] * 5 + [c_int, _P]),
     "maxsim_contrastive_forward_with_argmax": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, _P]),
     "maxsim_contrastive_backward": (c_int, [_P] * 7 + [_I64] * 5 + [c_int, _P]),
+    "maxsim_padded_backward_native": (c_int, [_P] * 8 + [_I64] * 5 + [c_int, _P]),
+    "maxsim_contrastive_backward_native": (c_int, [_P] * 7 + [_I64] * 5 + [c_int, _P]),
 }
 
 EXPORTED_SYMBOLS = tuple(_SIGNATURES)
@@ -561,6 +563,67 @@ def maxsim_padded_backward(dscore, queries, documents, query_lengths, doc_length
             _ptr(g), _ptr(q), _ptr(d), _ptr(qlen), _ptr(dlen), _ptr(a), _ptr(dq), _ptr(dd),
             B, C, Lq_max, Ld_max, q.shape[1], _code(q), _stream_ptr())
     _check(rc, "maxsim_padded_backward")
+    return dq, dd
+
+
+_EUNSUPPORTED = -2
+_native_grads = True
+
+
+def set_native_gradients(enabled: bool) -> None:
+    """Let the autograd functions ask the kernels for gradients in the inputs'
+    16-bit type (default) or always take the fp32 operators and autograd's cast."""
+    global _native_grads
+    _native_grads = bool(enabled)
+
+
+def padded_backward_native(dscore, queries, documents, query_lengths, doc_lengths, argmax,
+                           Lq_max, Ld_max, num_candidates):
+    """As ``maxsim_padded_backward`` but with both gradients in the inputs'
+    float16 / bfloat16 type (each row summed in fp32 and rounded once).
+    Returns None when the shape is not covered; the caller then uses the fp32
+    operator."""
+    if not _native_grads or queries.dtype not in (torch.float16, torch.bfloat16):
+        return None
+    dev = _require_cuda(queries, dscore, documents, query_lengths, doc_lengths, argmax)
+    q, qlen, d, dlen, B, C, Lq_max, Ld_max = _padded_args(
+        queries, query_lengths, documents, doc_lengths, Lq_max, Ld_max, num_candidates)
+    g = dscore.contiguous().to(torch.float32)
+    a = argmax.contiguous().to(torch.int32)
+    if g.numel() != B * C or tuple(a.shape) != (B * C, Lq_max) or B * C == 0:
+        return None
+    dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
+    dd = torch.empty(d.shape, dtype=d.dtype, device=dev)
+    with _on_device(dev):
+        rc = load_library().maxsim_padded_backward_native(
+            _ptr(g), _ptr(q), _ptr(d), _ptr(qlen), _ptr(dlen), _ptr(a), _ptr(dq), _ptr(dd),
+            B, C, Lq_max, Ld_max, q.shape[1], _code(q), _stream_ptr())
+    if rc == _EUNSUPPORTED:
+        return None
+    _check(rc, "maxsim_padded_backward_native")
+    return dq, dd
+
+
+def contrastive_backward_native(dscore, queries, documents, document_offsets, argmax):
+    """As ``maxsim_contrastive_backward`` with gradients in the inputs' 16-bit
+    type; None when the shape is not covered."""
+    if not _native_grads or queries.dtype not in (torch.float16, torch.bfloat16):
+        return None
+    dev = _require_cuda(queries, dscore, documents, document_offsets, argmax)
+    q, d, off, Nq, Lq, Nb, dim = _contrastive_args(queries, documents, document_offsets)
+    g = dscore.contiguous().to(torch.float32)
+    a = argmax.contiguous().to(torch.int32)
+    if tuple(g.shape) != (Nq, Nb) or tuple(a.shape) != (Nq, Nb, Lq) or Nq * Nb == 0:
+        return None
+    dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
+    dd = torch.empty(d.shape, dtype=d.dtype, device=dev)
+    with _on_device(dev):
+        rc = load_library().maxsim_contrastive_backward_native(
+            _ptr(g), _ptr(q), _ptr(d), _ptr(off), _ptr(a), _ptr(dq), _ptr(dd),
+            Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
+    if rc == _EUNSUPPORTED:
+        return None
+    _check(rc, "maxsim_contrastive_backward_native")
     return dq, dd
 
 

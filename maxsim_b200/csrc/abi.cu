@@ -227,7 +227,7 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
         fast = vec_ok && dim <= 128 && dim % 8 == 0 && d_rows < (1ll << 31);
         if (fast)
           bwd_dq_gather16_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq,
-                                                                                 q_rows);
+                                                                                 q_rows, 0);
       }
       if (!fast)
         bwd_dq_gather_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq,
@@ -252,7 +252,7 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
         // helps only when the mean document is that long.
         const int gy = (d_rows / Nb > kInvBins) ? 2 : 1;
         dim3 grid((unsigned)Nb, (unsigned)gy);
-        kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq);
+        kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 0);
         return launch_check("bwd_dd_invert_kernel");
       }
       MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
@@ -282,6 +282,64 @@ int run_backward(const PairTable& t, const float* dscore, const int32_t* argmax,
                                                   n_queries, n_documents);
     default: return run_backward_t<__nv_bfloat16, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st,
                                                   n_queries, n_documents);
+  }
+}
+
+// Gradients written once, in the inputs' 16-bit element type.  Only for the
+// shapes whose kernels store every gradient row exactly once; anything else is
+// MAXSIM_EUNSUPPORTED and the caller uses the fp32 operator.
+template <typename T, int LAYOUT>
+int run_backward_native_t(const PairTable& t, const float* dscore, const int32_t* argmax, void* dq,
+                          void* dd, int64_t q_rows, int64_t d_rows, int64_t Nq, cudaStream_t st) {
+  static_assert(LAYOUT == kPadded || LAYOUT == kContrastive, "padded and contrastive only");
+  const int dim = t.dim;
+  const bool ok = dim % 8 == 0 && dim <= 128 && aligned16(t.queries) && aligned16(t.documents) &&
+                  aligned16(dq) && aligned16(dd) && d_rows < (1ll << 31) && t.n_pairs > 0;
+  if (!ok) return fail(MAXSIM_EUNSUPPORTED, "native-type gradients need dim %% 8 == 0, dim <= 128 and aligned tensors");
+  const unsigned threads = kBwdWarps * 32;
+  if constexpr (LAYOUT == kPadded) {
+    if (t.q_slots > 32 || t.Ld_max > 1024)
+      return fail(MAXSIM_EUNSUPPORTED, "native-type gradients need Lq_max <= 32 and Ld_max <= 1024");
+  } else {
+    const int64_t Nb = t.C;
+    if ((int64_t)Nq * t.q_slots > kInvEntries || Nq > kInvMaxQ || Nb >= (1ll << 31))
+      return fail(MAXSIM_EUNSUPPORTED, "native-type gradients need Nq * Lq <= %d", kInvEntries);
+  }
+  {
+    const int64_t grid = (q_rows + kBwdWarps - 1) / kBwdWarps;
+    bwd_dq_gather16_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq, q_rows, 1);
+    if (int rc = launch_check("bwd_dq_gather16_kernel")) return rc;
+  }
+  if constexpr (LAYOUT == kPadded) {
+    const int64_t grid = (t.n_pairs + kBwdWarps - 1) / kBwdWarps;
+    bwd_dd_padded_native_kernel<T><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax,
+                                                                       reinterpret_cast<T*>(dd));
+    return launch_check("bwd_dd_padded_native_kernel");
+  } else {
+    const int64_t Nb = t.C;
+    auto kern = bwd_dd_invert_kernel<T>;
+    constexpr size_t smem = inv_smem_bytes();
+    static std::atomic<unsigned char> configured[kMaxDevices];
+    if (int rc = ensure_smem(kern, smem, configured)) return rc;
+    const int gy = (d_rows / Nb > kInvBins) ? 2 : 1;
+    dim3 grid((unsigned)Nb, (unsigned)gy);
+    kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 1);
+    return launch_check("bwd_dd_invert_kernel");
+  }
+}
+
+template <int LAYOUT>
+int run_backward_native(const PairTable& t, const float* dscore, const int32_t* argmax, void* dq,
+                        void* dd, int64_t q_rows, int64_t d_rows, int64_t Nq, int dtype,
+                        void* stream) {
+  if (t.dim <= 0 || t.q_slots <= 0 || t.n_pairs < 0 || q_rows < 0 || d_rows < 0)
+    return fail(MAXSIM_EINVAL, "sizes must be positive");
+  if (!dq || !dd || !dscore || !argmax) return fail(MAXSIM_EUNSUPPORTED, "empty problem");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (dtype) {
+    case MAXSIM_F16: return run_backward_native_t<__half, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
+    case MAXSIM_BF16: return run_backward_native_t<__nv_bfloat16, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
+    default: return fail(MAXSIM_EUNSUPPORTED, "native-type gradients are for float16 / bfloat16 inputs");
   }
 }
 
@@ -696,6 +754,19 @@ int maxsim_padded_backward(const float* dscore, const void* queries, const void*
                                B * C * Ld_max, B, dtype, stream);
 }
 
+int maxsim_padded_backward_native(const float* dscore, const void* queries, const void* documents,
+                                  const int32_t* query_lengths, const int32_t* doc_lengths,
+                                  const int32_t* argmax, void* grad_queries, void* grad_documents,
+                                  int64_t B, int64_t C, int64_t Lq_max, int64_t Ld_max,
+                                  int64_t dim, int dtype, void* stream) {
+  if (B < 0 || C < 0 || Lq_max <= 0 || Ld_max <= 0 || !fits_i32(dim) || !fits_i32(Lq_max) ||
+      !fits_i32(Ld_max) || !fits_i32(C))
+    return fail(MAXSIM_EINVAL, "Lq_max/Ld_max/num_candidates must all be > 0");
+  PairTable t = padded_table(queries, query_lengths, documents, doc_lengths, B, C, Lq_max, Ld_max, dim);
+  return run_backward_native<kPadded>(t, dscore, argmax, grad_queries, grad_documents, B * Lq_max,
+                                      B * C * Ld_max, B, dtype, stream);
+}
+
 int maxsim_contrastive_forward(const void* queries, const void* documents,
                                const int32_t* document_offsets, float* scores, int64_t Nq,
                                int64_t Lq, int64_t Nb, int64_t dim, int64_t total_d_tokens,
@@ -733,6 +804,21 @@ int maxsim_contrastive_backward(const float* dscore, const void* queries, const 
                                   total_d_tokens);
   return run_backward<kContrastive>(t, dscore, argmax, grad_queries, grad_documents, Nq * Lq,
                                     total_d_tokens, Nq, dtype, stream);
+}
+
+int maxsim_contrastive_backward_native(const float* dscore, const void* queries,
+                                       const void* documents, const int32_t* document_offsets,
+                                       const int32_t* argmax, void* grad_queries,
+                                       void* grad_documents, int64_t Nq, int64_t Lq, int64_t Nb,
+                                       int64_t dim, int64_t total_d_tokens, int dtype,
+                                       void* stream) {
+  if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
+      !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
+  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim,
+                                  total_d_tokens);
+  return run_backward_native<kContrastive>(t, dscore, argmax, grad_queries, grad_documents,
+                                           Nq * Lq, total_d_tokens, Nq, dtype, stream);
 }
 
 }  // extern "C"

@@ -18,6 +18,8 @@
 //     otherwise vector reductions (red.global.add) after a zero fill.
 #pragma once
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace maxsim {
@@ -84,6 +86,28 @@ struct Row8<float> {
     acc[6] = fmaf(g, b.z, acc[6]); acc[7] = fmaf(g, b.w, acc[7]);
   }
 };
+
+// Store eight consecutive gradient elements, either as fp32 (the operators'
+// contract) or rounded once to the inputs' 16-bit type (what autograd's cast of
+// the fp32 gradient would produce, without the extra pass over memory).
+template <typename T>
+__device__ __forceinline__ void store8(void* row_base, int k, const float (&acc)[8], bool native) {
+  if (native) {
+    if constexpr (sizeof(T) == 2) {
+      T h[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if constexpr (std::is_same<T, __half>::value) h[e] = __float2half_rn(acc[e]);
+        else h[e] = __float2bfloat16_rn(acc[e]);
+      }
+      *reinterpret_cast<uint4*>(reinterpret_cast<T*>(row_base) + k) = *reinterpret_cast<const uint4*>(h);
+      return;
+    }
+  }
+  float4* out = reinterpret_cast<float4*>(reinterpret_cast<float*>(row_base) + k);
+  out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
+  out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+}
 
 // ---------------------------------------------------------------------------
 // grad_q by gather (padded: over the C candidates of query b; contrastive:
@@ -172,8 +196,8 @@ bwd_dq_gather_kernel(PairTable t, const float* __restrict__ dscore,
 template <typename T, int LAYOUT>
 __global__ void __launch_bounds__(kBwdWarps * 32)
 bwd_dq_gather16_kernel(PairTable t, const float* __restrict__ dscore,
-                       const int32_t* __restrict__ argmax, float* __restrict__ dq,
-                       int64_t n_rows) {
+                       const int32_t* __restrict__ argmax, void* __restrict__ dq,
+                       int64_t n_rows, int native) {
   static_assert(sizeof(T) == 2, "16-bit element types only");
   const int lane = threadIdx.x & 31, half = lane >> 4, hl = lane & 15;
   const int64_t row = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
@@ -232,9 +256,9 @@ bwd_dq_gather16_kernel(PairTable t, const float* __restrict__ dscore,
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
   if (half == 0 && k_ok) {
-    float4* out = reinterpret_cast<float4*>(dq + row * dim + k);
-    out[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    out[1] = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    void* row_base = native ? static_cast<void*>(reinterpret_cast<T*>(dq) + row * dim)
+                            : static_cast<void*>(reinterpret_cast<float*>(dq) + row * dim);
+    store8<T>(row_base, k, acc, native != 0);
   }
 }
 
@@ -282,6 +306,74 @@ bwd_dd_padded_kernel(PairTable t, const float* __restrict__ dscore,
       store4(dst, vec, k, dim, cur);
     }
     // the same lane owns the same dims of every row: no cross-lane hazard
+  }
+}
+
+// grad_d of the padded layout, rows written once in the inputs' 16-bit type.
+// One warp per slab, for Lq_max <= 32 and Ld_max <= 1024: lane i holds the
+// winning token of query token i; tokens that won the same document token are
+// found with a warp match, their query rows are summed in registers and the
+// row is stored once, rounded once; rows nobody won are zero-filled from a
+// bitmap.  Same values as casting the fp32 operator's result, without its
+// read-modify-writes, its fp32 tensor and the cast's pass over it.
+template <typename T>
+__global__ void __launch_bounds__(kBwdWarps * 32)
+bwd_dd_padded_native_kernel(PairTable t, const float* __restrict__ dscore,
+                            const int32_t* __restrict__ argmax, T* __restrict__ dd) {
+  static_assert(sizeof(T) == 2, "16-bit element types only");
+  const int lane = threadIdx.x & 31;
+  const int64_t p = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
+  if (p >= t.n_pairs) return;
+  const int dim = t.dim, slots = t.q_slots, Ld_max = t.Ld_max;
+  const PairGeom g = pair_geom<kPadded>(t, p);
+  T* slab = dd + p * (int64_t)Ld_max * dim;
+  const float gv = __ldg(dscore + p);
+  const T* Q = reinterpret_cast<const T*>(t.queries) + g.q_row0 * dim;
+
+  int jl = -1;
+  if (lane < g.Lq) {
+    jl = __ldg(argmax + p * slots + lane);
+    if (jl < 0 || jl >= g.Ld) jl = -1;
+  }
+  const unsigned same = __match_any_sync(0xffffffffu, jl);
+  const bool leader = jl >= 0 && lane == (__ffs(same) - 1);
+  unsigned leaders = __ballot_sync(0xffffffffu, leader);
+  uint32_t written = 0u;  // lane w: rows 32w .. 32w+31
+  while (leaders) {
+    const int l = __ffs(leaders) - 1;
+    leaders &= leaders - 1;
+    const int j = __shfl_sync(0xffffffffu, jl, l);
+    unsigned members = __shfl_sync(0xffffffffu, same, l);
+    if (lane == (j >> 5)) written |= 1u << (j & 31);
+    for (int k = lane * 4; k < dim; k += 128) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      unsigned mm = members;
+      while (mm) {
+        const int i = __ffs(mm) - 1;
+        mm &= mm - 1;
+        float qv[4];
+        load4<T>(Q + (int64_t)i * dim, true, k, dim, qv);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = fmaf(gv, qv[e], acc[e]);  // same order as the fp32 kernel
+      }
+      T h[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        if constexpr (std::is_same<T, __half>::value) h[e] = __float2half_rn(acc[e]);
+        else h[e] = __float2bfloat16_rn(acc[e]);
+      }
+      *reinterpret_cast<uint2*>(slab + (int64_t)j * dim + k) = *reinterpret_cast<const uint2*>(h);
+    }
+  }
+  for (int w = 0; w * 32 < Ld_max; ++w) {
+    uint32_t missing = ~__shfl_sync(0xffffffffu, written, w);
+    if (Ld_max - w * 32 < 32) missing &= (1u << (Ld_max - w * 32)) - 1u;
+    while (missing) {
+      const int r = w * 32 + __ffs(missing) - 1;
+      missing &= missing - 1;
+      for (int k = lane * 4; k < dim; k += 128)
+        *reinterpret_cast<uint2*>(slab + (int64_t)r * dim + k) = make_uint2(0u, 0u);
+    }
   }
 }
 
@@ -554,7 +646,11 @@ constexpr size_t inv_smem_bytes() {
 template <typename T>
 __global__ void __launch_bounds__(kInvThreads, 1)
 bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
-                     const int32_t* __restrict__ argmax, float* __restrict__ dd, int Nq) {
+                     const int32_t* __restrict__ argmax, void* __restrict__ dd_out, int Nq,
+                     int native) {
+  // `native` (rows stored once, in the inputs' type) is only given when all
+  // entries of a document fit one pass; the fp32 form adds later passes in place.
+  float* dd = reinterpret_cast<float*>(dd_out);
   extern __shared__ __align__(16) unsigned char inv_smem[];
   int32_t* list = reinterpret_cast<int32_t*>(inv_smem);                 // [kInvEntries]
   float* gcol = reinterpret_cast<float*>(list + kInvEntries);          // [kInvMaxQ]
@@ -684,7 +780,9 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
           }
 #pragma unroll
           for (int x = 0; x < 8; ++x) acc[x] += __shfl_xor_sync(0xffffffffu, acc[x], 16);
-          if (half == 0 && k_ok) {
+          if (half == 0 && k_ok && native) {
+            store8<T>(reinterpret_cast<T*>(dd_out) + ((int64_t)d0 + tok0 + j) * dim, k, acc, true);
+          } else if (half == 0 && k_ok) {
             float4* o4 = reinterpret_cast<float4*>(out + k);
             if (q0 == 0) {
               o4[0] = make_float4(acc[0], acc[1], acc[2], acc[3]);
