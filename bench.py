@@ -563,33 +563,52 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
                      for r in range(world)]
     target = mdist.contrastive_targets(q1 - q0, device=dev, docs_per_rank=docs_per_rank)
 
-    def step():
-        q.grad = None
-        d.grad = None
-        s = mdist.score_contrastive_sharded(q, d, lens)
-        torch.nn.functional.cross_entropy(s, target).backward()
+    lens_host = data["doc_lengths_all"].cpu()
+    shard_sizes = []
+    for r in range(world):
+        a0, a1 = mdist.shard_range(n, r, world)
+        shard_sizes.append((int(lens_host[a0:a1].sum()), a1 - a0, a1 - a0))
 
-    for _ in range(3):
-        step()
-    torch.cuda.synchronize()
-    dist.barrier()
-    iters = 10
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(iters):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+    def timed(exchange, sizes=None):
+        def step():
+            q.grad = None
+            d.grad = None
+            s = mdist.score_contrastive_sharded(q, d, lens, exchange=exchange, shard_sizes=sizes)
+            torch.nn.functional.cross_entropy(s, target).backward()
+
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+        dist.barrier()
+        iters = 10
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    ms_rs = timed("reduce_scatter")
+    ms_owner = timed("owner")
+    ms = timed("owner", shard_sizes)
     T = int(data["doc_lengths_all"].sum().item())
     flops = 2 * 128 * n * 32 * T + 4 * 128 * n * n * 32
     return {"c5_contrastive_train_bf16_sharded": {
         "ms_per_step": ms, "pairs_per_s": n * n / (ms * 1e-3),
         "tensor_frac_all_gpus": flops / (ms * 1e-3) / (world * peaks["bf16_tflops"] * 1e12),
-        "note": f"global Nq=Nb={n} over {world} ranks (strong scaling); all-gather documents, "
-                "one launch over the gathered buffer, reduce-scatter of grad_documents; max over ranks"}}
+        "ms_per_step_sizes_exchanged_in_step": ms_owner,
+        "ms_per_step_reduce_scatter": ms_rs,
+        "note": f"global Nq=Nb={n} over {world} ranks (strong scaling); all-gather documents, one "
+                "forward launch over the gathered buffer; backward: grad_queries locally, each owner "
+                "receives the argmax / score-gradient records of its documents (all-to-all) and the "
+                "all-gathered queries and computes its grad_documents; every rank's shard sizes are "
+                "passed in (known to the data pipeline), so the host never waits for the device; "
+                "ms_per_step_sizes_exchanged_in_step = the same with the sizes all-gathered and read "
+                "back inside the step; ms_per_step_reduce_scatter = "
+                "the variant that reduce-scatters fp32 partial grad_documents; max over ranks"}}
 
 
 def run_contrastive_profile(args):

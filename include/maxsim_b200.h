@@ -310,7 +310,10 @@ MAXSIM_API int maxsim_contrastive_forward_with_argmax(
 
 /* Replaces maxsim_contrastive_backward (maxsim_cuda/maxsim.cu:1856-1920).
  * dscore [Nq, Nb]; grad_queries [Nq, Lq, dim], grad_documents
- * [total_d_tokens, dim]. */
+ * [total_d_tokens, dim].  Extension: either gradient pointer may be NULL, in
+ * which case that gradient is not computed (the multi-GPU driver computes
+ * grad_queries on the rank that holds the queries and grad_documents on the
+ * rank that owns the documents). */
 MAXSIM_API int maxsim_contrastive_backward(
     const float* dscore,
     const void* queries, const void* documents,

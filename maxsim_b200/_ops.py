@@ -684,6 +684,29 @@ def maxsim_contrastive_forward_with_argmax(queries, documents, document_offsets)
     return scores, argmax
 
 
+def contrastive_backward_part(dscore, queries, documents, document_offsets, argmax, *,
+                              want_queries: bool, want_documents: bool):
+    """``maxsim_contrastive_backward`` computing only the requested gradients
+    (fp32); the other entry of the returned pair is None."""
+    dev = _require_cuda(queries, dscore, documents, document_offsets, argmax)
+    q, d, off, Nq, Lq, Nb, dim = _contrastive_args(queries, documents, document_offsets)
+    g = dscore.contiguous().to(torch.float32)
+    a = argmax.contiguous().to(torch.int32)
+    if tuple(g.shape) != (Nq, Nb):
+        raise RuntimeError("dscore must have shape [Nq, Nb]")
+    if tuple(a.shape) != (Nq, Nb, Lq):
+        raise RuntimeError("argmax must have shape [Nq, Nb, Lq]")
+    dq = torch.empty(q.shape, dtype=torch.float32, device=dev) if want_queries else None
+    dd = torch.empty(d.shape, dtype=torch.float32, device=dev) if want_documents else None
+    with _on_device(dev):
+        rc = load_library().maxsim_contrastive_backward(
+            _ptr(g), _ptr(q), _ptr(d), _ptr(off), _ptr(a),
+            _ptr(dq) if dq is not None else 0, _ptr(dd) if dd is not None else 0,
+            Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
+    _check(rc, "maxsim_contrastive_backward")
+    return dq, dd
+
+
 def maxsim_contrastive_backward(dscore, queries, documents, document_offsets, argmax):
     dev = _require_cuda(queries, dscore, documents, document_offsets, argmax)
     q, d, off, Nq, Lq, Nb, dim = _contrastive_args(queries, documents, document_offsets)

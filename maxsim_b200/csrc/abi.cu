@@ -216,11 +216,11 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
     return launch_check("bwd_route_atomic_kernel");
   } else {
     if (t.n_pairs == 0) {
-      MAXSIM_CUDA(cudaMemsetAsync(dq, 0, (size_t)q_rows * dim * sizeof(float), st));
-      MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
+      if (dq) MAXSIM_CUDA(cudaMemsetAsync(dq, 0, (size_t)q_rows * dim * sizeof(float), st));
+      if (dd) MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
       return MAXSIM_OK;
     }
-    {
+    if (dq) {
       const int64_t grid = (q_rows + kBwdWarps - 1) / kBwdWarps;
       bool fast = false;
       if constexpr (sizeof(T) == 2) {
@@ -240,6 +240,7 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
       bwd_dd_padded_kernel<T><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dd, vec_ok);
       return launch_check("bwd_dd_padded_kernel");
     } else {
+      if (!dd) return MAXSIM_OK;
       const int64_t Nb = t.C;
       if (vec_ok && dim % 8 == 0 && t.q_slots <= kInvEntries && Nq < (1ll << 31) &&
           Nb < (1ll << 31) && Nq * (int64_t)t.q_slots < (1ll << 31)) {
@@ -271,7 +272,12 @@ int run_backward(const PairTable& t, const float* dscore, const int32_t* argmax,
   if (!valid_dtype(dtype)) return fail(MAXSIM_EINVAL, "unknown dtype code %d", dtype);
   if (t.dim <= 0 || t.q_slots <= 0 || t.n_pairs < 0 || q_rows < 0 || d_rows < 0)
     return fail(MAXSIM_EINVAL, "sizes must be positive");
-  if ((q_rows && !dq) || (d_rows && !dd)) return fail(MAXSIM_EINVAL, "null gradient pointer");
+  // The contrastive operator may be asked for one gradient only (the other
+  // pointer NULL): the sharded driver computes grad_queries where the queries
+  // live and grad_documents where the documents live.
+  if (LAYOUT != kContrastive && ((q_rows && !dq) || (d_rows && !dd)))
+    return fail(MAXSIM_EINVAL, "null gradient pointer");
+  if (LAYOUT == kContrastive && !dq && !dd) return MAXSIM_OK;
   if (t.n_pairs && (!dscore || !argmax || !t.queries || !t.documents))
     return fail(MAXSIM_EINVAL, "null pointer argument");
   cudaStream_t st = static_cast<cudaStream_t>(stream);

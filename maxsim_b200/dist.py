@@ -56,8 +56,11 @@ def offsets_from_lengths(lengths: torch.Tensor) -> torch.Tensor:
 
 
 def _default_ops():
-    from ._ops import ops
-    return ops
+    import types
+
+    from . import _ops
+    return types.SimpleNamespace(**vars(_ops.ops),
+                                 contrastive_backward_part=_ops.contrastive_backward_part)
 
 
 def _world(group) -> Tuple[int, int]:
@@ -98,7 +101,8 @@ def score_candidates_padded_sharded(queries, documents, query_lengths, doc_lengt
 # Contrastive training: all-gather documents, per-owner gradient reduction
 # ---------------------------------------------------------------------------
 
-def _gather_shards(documents: torch.Tensor, lengths: torch.Tensor, group, world: int):
+def _gather_shards(documents: torch.Tensor, lengths: torch.Tensor, group, world: int,
+                   n_queries: int = 0, shard_sizes=None):
     """All-gather ragged packed shards into one buffer.
 
     Every shard is padded to ``t_pad = longest shard + 1`` token rows, so the
@@ -108,16 +112,25 @@ def _gather_shards(documents: torch.Tensor, lengths: torch.Tensor, group, world:
     rank r's real documents followed by one filler document that covers its
     padding rows.  Returns the buffer, the combined int32 offsets, the column
     indices of the real (non-filler) documents, the number of columns, the
-    per-rank ``(tokens, documents)`` sizes and ``t_pad``."""
+    per-rank ``(tokens, documents, queries)`` sizes and ``t_pad``."""
     dev = documents.device
     nccl = dist.get_backend(group) == "nccl"
-    meta = torch.tensor([documents.shape[0], lengths.numel()], dtype=torch.int64, device=dev)
-    metas = torch.empty((world, 2), dtype=torch.int64, device=dev)
-    if nccl:
-        dist.all_gather_into_tensor(metas, meta, group=group)
+    if shard_sizes is not None:
+        # the caller already knows every rank's (tokens, documents, queries): no
+        # exchange and, above all, no wait for the device on the host
+        sizes = [(int(t), int(n), int(nq)) for t, n, nq in shard_sizes]
+        rank = dist.get_rank(group)
+        if len(sizes) != world or sizes[rank] != (documents.shape[0], lengths.numel(), n_queries):
+            raise ValueError(f"shard_sizes[{rank}] = {sizes[rank] if len(sizes) == world else None} does not "
+                             f"describe this rank's shard {(documents.shape[0], lengths.numel(), n_queries)}")
     else:
-        dist.all_gather(list(metas.unbind(0)), meta, group=group)
-    sizes = [(int(t), int(n)) for t, n in metas.tolist()]  # one transfer for all ranks
+        meta = torch.tensor([documents.shape[0], lengths.numel(), n_queries], dtype=torch.int64, device=dev)
+        metas = torch.empty((world, 3), dtype=torch.int64, device=dev)
+        if nccl:
+            dist.all_gather_into_tensor(metas, meta, group=group)
+        else:
+            dist.all_gather(list(metas.unbind(0)), meta, group=group)
+        sizes = [(int(t), int(n), int(nq)) for t, n, nq in metas.tolist()]  # one transfer for all ranks
     t_pad = max(s[0] for s in sizes) + 1
     n_max = max(s[1] for s in sizes)
 
@@ -169,43 +182,113 @@ def _reduce_scatter_rows(full: torch.Tensor, world: int, rank: int, group) -> to
     return full[rank * t_pad:(rank + 1) * t_pad]
 
 
+def _all_gather_rows(x: torch.Tensor, rows_per_rank: Sequence[int], group, world: int) -> torch.Tensor:
+    """Concatenate every rank's ``x [rows_r, ...]`` along dim 0 (``rows_r`` may differ)."""
+    n_max = max(rows_per_rank)
+    pad = x
+    if x.shape[0] != n_max:
+        pad = x.new_zeros((n_max,) + tuple(x.shape[1:]))
+        pad[: x.shape[0]] = x
+    out = torch.empty((world * n_max,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(out, pad.contiguous(), group=group)
+    else:
+        dist.all_gather(list(out.view((world, n_max) + tuple(x.shape[1:])).unbind(0)), pad.contiguous(),
+                        group=group)
+    if all(n == n_max for n in rows_per_rank):
+        return out
+    parts = out.view((world, n_max) + tuple(x.shape[1:]))
+    return torch.cat([parts[r, : rows_per_rank[r]] for r in range(world)], dim=0)
+
+
+def _columns_to_owners(x: torch.Tensor, docs_per_rank: Sequence[int], queries_per_rank: Sequence[int],
+                       rank: int, group) -> torch.Tensor:
+    """``x [Nq_local, Nb_total, W]`` holds, for this rank's queries, one record
+    of W ints per document column (columns in rank order).  Every owner gets
+    the records of its own documents from all ranks: returns
+    ``[Nq_total, Nb_own, W]`` with queries in rank order."""
+    nq_local, _, width = x.shape
+    send = x.transpose(0, 1).contiguous().view(-1)                 # [Nb_total, Nq_local, W]
+    in_splits = [n * nq_local * width for n in docs_per_rank]
+    n_own = docs_per_rank[rank]
+    out_splits = [n_own * nq * width for nq in queries_per_rank]
+    recv = torch.empty((sum(out_splits),), dtype=x.dtype, device=x.device)
+    dist.all_to_all_single(recv, send, out_splits, in_splits, group=group)
+    blocks, at = [], 0
+    for nq, n in zip(queries_per_rank, out_splits):
+        blocks.append(recv[at:at + n].view(n_own, nq, width).transpose(0, 1))
+        at += n
+    return torch.cat(blocks, dim=0).contiguous()
+
+
 class _ShardedContrastive(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, queries, documents, doc_lengths, group, ops):
+    def forward(ctx, queries, documents, doc_lengths, group, ops, exchange, shard_sizes):
         rank, world = _world(group)
         q = queries.contiguous()
         d_local = documents.contiguous()
         lens_local = doc_lengths.to(torch.int32).contiguous()
+        sizes = None
         if world == 1:
             docs_all, offsets, real, n_cols = d_local, offsets_from_lengths(lens_local), None, 0
             t_pad = d_local.shape[0]
         else:
-            docs_all, offsets, real, n_cols, _sizes, t_pad = _gather_shards(d_local, lens_local,
-                                                                            group, world)
+            docs_all, offsets, real, n_cols, sizes, t_pad = _gather_shards(
+                d_local, lens_local, group, world, n_queries=q.shape[0], shard_sizes=shard_sizes)
         scores_all, argmax = ops.maxsim_contrastive_forward_with_argmax(q, docs_all, offsets)
-        ctx.save_for_backward(q, docs_all, offsets, argmax)
-        ctx.real, ctx.n_cols = real, n_cols
+        ctx.save_for_backward(q, docs_all, offsets, argmax, d_local, lens_local)
+        ctx.real, ctx.n_cols, ctx.sizes = real, n_cols, sizes
         ctx.group, ctx.ops, ctx.rank, ctx.world = group, ops, rank, world
-        ctx.t_local, ctx.t_pad = d_local.shape[0], t_pad
+        ctx.t_local, ctx.t_pad, ctx.exchange = d_local.shape[0], t_pad, exchange
         return scores_all if real is None else scores_all.index_select(1, real)
 
     @staticmethod
     def backward(ctx, dscore):
-        q, docs_all, offsets, argmax = ctx.saved_tensors
+        q, docs_all, offsets, argmax, d_local, lens_local = ctx.saved_tensors
         ops, group, rank, world = ctx.ops, ctx.group, ctx.rank, ctx.world
+        part = getattr(ops, "contrastive_backward_part", None)
         g = dscore.contiguous().to(torch.float32)
-        if ctx.real is not None:  # filler documents receive no gradient
-            g_all = torch.zeros((g.shape[0], ctx.n_cols), dtype=torch.float32, device=g.device)
-            g_all.index_copy_(1, ctx.real, g)
-            g = g_all
-        dq, dd_all = ops.maxsim_contrastive_backward(g, q, docs_all, offsets, argmax)
         if world == 1:
-            return dq, dd_all, None, None, None
-        mine = _reduce_scatter_rows(dd_all, world, rank, group)
-        return dq, mine[: ctx.t_local].contiguous(), None, None, None
+            dq, dd_all = ops.maxsim_contrastive_backward(g, q, docs_all, offsets, argmax)
+            return dq, dd_all, None, None, None, None, None
+        # filler documents receive no gradient
+        g_all = torch.zeros((g.shape[0], ctx.n_cols), dtype=torch.float32, device=g.device)
+        g_all.index_copy_(1, ctx.real, g)
+
+        if ctx.exchange == "reduce_scatter":
+            dq, dd_all = ops.maxsim_contrastive_backward(g_all, q, docs_all, offsets, argmax)
+            mine = _reduce_scatter_rows(dd_all, world, rank, group)
+            return dq, mine[: ctx.t_local].contiguous(), None, None, None, None, None
+
+        # "owner": grad_queries is computed here, where the queries are.  For
+        # grad_documents every rank sends each owner the argmax and the score
+        # gradient of that owner's documents (one int32 record of Lq + 1 words
+        # per pair) and the queries are all-gathered; each owner then computes
+        # the gradient of its own documents from all queries.  This moves
+        # 4 * (Lq + 1) bytes per pair instead of 4 * dim bytes per document
+        # token per rank, and no partial sums.
+        if part is not None:
+            dq = part(g_all, q, docs_all, offsets, argmax, want_queries=True, want_documents=False)[0]
+        else:
+            dq = ops.maxsim_contrastive_backward(g_all, q, docs_all, offsets, argmax)[0]
+        docs_per_rank = [s[1] for s in ctx.sizes]
+        queries_per_rank = [s[2] for s in ctx.sizes]
+        record = torch.cat([argmax.index_select(1, ctx.real).to(torch.int32),
+                            g.view(torch.int32).unsqueeze(-1)], dim=2)      # [Nq_local, Nb_total, Lq + 1]
+        mine = _columns_to_owners(record, docs_per_rank, queries_per_rank, rank, group)
+        a_own = mine[:, :, :-1].contiguous()
+        g_own = mine[:, :, -1].contiguous().view(torch.float32)
+        q_all = _all_gather_rows(q, queries_per_rank, group, world)
+        off_local = offsets_from_lengths(lens_local)
+        if part is not None:
+            dd = part(g_own, q_all, d_local, off_local, a_own, want_queries=False, want_documents=True)[1]
+        else:
+            dd = ops.maxsim_contrastive_backward(g_own, q_all, d_local, off_local, a_own)[1]
+        return dq, dd, None, None, None, None, None
 
 
-def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, ops=None):
+def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, ops=None,
+                              exchange: str = "owner", shard_sizes=None):
     """Differentiable contrastive scores of this rank's queries against the
     documents of all ranks.
 
@@ -217,6 +300,17 @@ def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, op
     Returns:
         ``[Nq_local, Nb_total]`` fp32, document columns in rank order.  The
         gradient reaching ``documents`` is the sum over all ranks' queries.
+
+    ``shard_sizes``, when given, is the list of every rank's ``(document
+    tokens, documents, queries)`` in rank order (a data pipeline can exchange
+    these numbers ahead of the step): the driver then neither exchanges them
+    nor waits for the device, so the host keeps launching ahead of the GPU.
+
+    ``exchange`` selects how the backward pass gets that sum to the owner:
+    ``"owner"`` (default) sends each owner the argmax and score gradient of its
+    documents and lets it compute the gradient from the all-gathered queries;
+    ``"reduce_scatter"`` has every rank compute a partial gradient for all
+    documents and reduce-scatters the partial sums.
     """
     if ops is None:
         ops = _default_ops()
@@ -228,7 +322,9 @@ def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, op
         raise ValueError("queries must be [Nq, Lq, D] and documents [T, D] with matching D")
     if queries.dtype != documents.dtype:
         raise TypeError(f"queries and documents must share dtype; got {queries.dtype} and {documents.dtype}")
-    return _ShardedContrastive.apply(queries, documents, doc_lengths, group, ops)
+    if exchange not in ("owner", "reduce_scatter"):
+        raise ValueError(f"exchange must be 'owner' or 'reduce_scatter'; got {exchange!r}")
+    return _ShardedContrastive.apply(queries, documents, doc_lengths, group, ops, exchange, shard_sizes)
 
 
 def contrastive_targets(n_queries_local: int, *, group=None, device=None,

@@ -61,7 +61,7 @@ def _init(rank, world, port, timeout_s=60):
                             timeout=timedelta(seconds=timeout_s))
 
 
-def _contrastive_worker(rank, world, port, out_dir):
+def _contrastive_worker(rank, world, port, out_dir, exchange):
     _init(rank, world, port)
     try:
         wl = W.c5_contrastive_ties_bf16(seed=31, Nq=12, Nb=11, Lq=16, dim=32, lo=3, hi=40)
@@ -71,7 +71,15 @@ def _contrastive_worker(rank, world, port, out_dir):
         t0, t1 = int(wl.document_offsets[d0]), int(wl.document_offsets[d1])
         q = torch.from_numpy(wl.queries[q0:q1]).requires_grad_(True)
         d = torch.from_numpy(wl.documents[t0:t1]).requires_grad_(True)
-        s = mdist.score_contrastive_sharded(q, d, torch.from_numpy(lens[d0:d1]), ops=_oracle_ops())
+        sizes = None
+        if exchange == "owner" and world == 3:  # also the path where the caller supplies the shard sizes
+            sizes = []
+            for r in range(world):
+                a0, a1 = mdist.shard_range(11, r, world)
+                b0, b1 = mdist.shard_range(12, r, world)
+                sizes.append((int(wl.document_offsets[a1] - wl.document_offsets[a0]), a1 - a0, b1 - b0))
+        s = mdist.score_contrastive_sharded(q, d, torch.from_numpy(lens[d0:d1]), ops=_oracle_ops(),
+                                            exchange=exchange, shard_sizes=sizes)
         g = torch.from_numpy(np.random.default_rng(5).standard_normal((12, 11)).astype(np.float32))
         (s * g[q0:q1]).sum().backward()
         docs_per_rank = [mdist.shard_range(11, r, world)[1] - mdist.shard_range(11, r, world)[0]
@@ -83,11 +91,12 @@ def _contrastive_worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 3])
-def test_contrastive_sharded_matches_unsharded(world, tmp_path):
+@pytest.mark.parametrize("world,exchange", [(2, "owner"), (3, "owner"), (5, "owner"),  # 5: uneven query shards
+                                            (2, "reduce_scatter"), (3, "reduce_scatter")])
+def test_contrastive_sharded_matches_unsharded(world, exchange, tmp_path):
     from oracle import maxsim_oracle as oracle
     port = _free_port()
-    mp.spawn(_contrastive_worker, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    mp.spawn(_contrastive_worker, args=(world, port, str(tmp_path), exchange), nprocs=world, join=True)
     wl = W.c5_contrastive_ties_bf16(seed=31, Nq=12, Nb=11, Lq=16, dim=32, lo=3, hi=40)
     ws, wa = oracle.score_contrastive(wl.queries, wl.documents, wl.document_offsets)
     g = np.random.default_rng(5).standard_normal((12, 11)).astype(np.float32)

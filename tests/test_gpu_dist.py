@@ -50,9 +50,16 @@ def _worker(rank, world, port, out_dir):
         q = part["queries"].clone().requires_grad_(True)
         d = part["documents"].clone().requires_grad_(True)
         lens = full["doc_lengths_all"][d0:d1].to(dev)
-        s = mdist.score_contrastive_sharded(q, d, lens)
         g = torch.randn(n, n, generator=torch.Generator().manual_seed(3)).to(dev)
+        # both ways of getting grad_documents to its owner
+        q_rs = part["queries"].clone().requires_grad_(True)
+        d_rs = part["documents"].clone().requires_grad_(True)
+        s_rs = mdist.score_contrastive_sharded(q_rs, d_rs, lens, exchange="reduce_scatter")
+        (s_rs * g[q0:q1]).sum().backward()
+        s = mdist.score_contrastive_sharded(q, d, lens, exchange="owner")
         (s * g[q0:q1]).sum().backward()
+        assert torch.equal(s, s_rs) and torch.equal(q.grad, q_rs.grad)
+        torch.testing.assert_close(d.grad.float(), d_rs.grad.float(), rtol=2e-2, atol=2e-2)
         # the same thing on this GPU alone
         qf = full["queries"].clone().requires_grad_(True)
         df = full["documents"].clone().requires_grad_(True)
