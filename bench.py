@@ -534,13 +534,25 @@ def bench_reference_matrix(dev):
                     def step():
                         return maxsim.score_pairs_packed(qf, qoff, df, doff, qids, dids, max_q_len=Lq)
             ms = timed(step)
-            rows.append({"name": name, "dtype": dname, "shape": shp, "ms": round(ms, 4),
-                         "reference_h200_ms": ref_ms, "ratio": round(ref_ms / ms, 2)})
+            row = {"name": name, "dtype": dname, "shape": shp, "ms": round(ms, 4),
+                   "reference_h200_ms": ref_ms, "ratio": round(ref_ms / ms, 2)}
+            if kind == "contrastive":
+                # the same training step (in-batch cross-entropy instead of a plain sum)
+                # replayed from a CUDA graph, input copies into the static buffers included
+                try:
+                    stepper = maxsim.GraphedContrastiveStep(shp["Nq"], shp["Lq"], shp["Nb"], shp["dim"],
+                                                            shp["Nb"] * shp["Ld"] + 64, dtype=dtype, device=dev)
+                    row["graphed_step_ms"] = round(timed(lambda: stepper.step(q, docs, cu)), 4)
+                    del stepper
+                except Exception as exc:  # report, do not fail the benchmark
+                    row["graphed_step_ms"] = f"unavailable: {type(exc).__name__}"
+            rows.append(row)
     return {"rows": rows,
             "note": "the reference's benchmark matrix with its timing method (per-iteration CUDA events "
                     "and synchronise, median of 30, Python wrapper and input clones included); "
                     "reference_h200_ms are the reference's published H200 figures (other hardware), "
-                    "ratio = reference_h200_ms / ms"}
+                    "ratio = reference_h200_ms / ms; graphed_step_ms = GraphedContrastiveStep.step "
+                    "(loss + both gradients replayed from a CUDA graph) on the same batch"}
 
 
 def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):

@@ -75,3 +75,31 @@ def test_contrastive_train_step_replays_from_a_graph():
     fresh = step()
     torch.testing.assert_close(loss, fresh[0].detach(), rtol=1e-6, atol=1e-6)
     assert _ops.device_status() == 0
+
+
+def test_graphed_contrastive_step_follows_batches_of_different_token_counts():
+    torch.manual_seed(0)
+    Nq, Lq, Nb, dim = 16, 32, 12, 128
+    stepper = maxsim.GraphedContrastiveStep(Nq, Lq, Nb, dim, token_capacity=2000,
+                                            dtype=torch.bfloat16, device=DEV, temperature=0.5)
+    for it, hi in enumerate([20, 150, 60]):      # batches with different packed token counts
+        lens = torch.randint(3, hi, (Nb,))
+        off = torch.zeros(Nb + 1, dtype=torch.int32)
+        off[1:] = lens.cumsum(0)
+        q = torch.nn.functional.normalize(torch.randn(Nq, Lq, dim), dim=-1).to(DEV, torch.bfloat16)
+        d = torch.nn.functional.normalize(torch.randn(int(off[-1]), dim), dim=-1).to(DEV, torch.bfloat16)
+        targets = torch.randint(0, Nb, (Nq,), device=DEV) if it == 2 else None
+        loss, gq, gd = stepper.step(q, d, off.to(DEV), targets)
+        # the same step, eagerly
+        qe, de = q.clone().requires_grad_(True), d.clone().requires_grad_(True)
+        s = maxsim.score_contrastive_train(qe, de, off.to(DEV))
+        want = torch.nn.functional.cross_entropy(
+            s / 0.5, targets if targets is not None else torch.arange(Nq, device=DEV) % Nb)
+        want.backward()
+        torch.testing.assert_close(loss, want, rtol=1e-5, atol=1e-6)
+        assert gd.shape == d.shape and gq.dtype == torch.bfloat16
+        assert torch.equal(gq, qe.grad)
+        torch.testing.assert_close(gd.float(), de.grad.float(), rtol=2.0 ** -6, atol=1e-4)
+    with pytest.raises(ValueError, match="documents must be"):
+        stepper.step(q, torch.zeros(2000, dim, device=DEV, dtype=torch.bfloat16), off.to(DEV))
+    assert _ops.device_status() == 0
