@@ -160,12 +160,13 @@ int run_forward(const PairTable& t, float* scores, int32_t* argmax, int dtype, v
     int variant = 0;
     if (path == 5 && (t.n_pairs / t.C) >= 16) variant = 1;
     if (path == 6) variant = 2;
+    if (path == 7) variant = 3;  // the earlier epilogue, for comparison
     const int rc = launch_tc05<ARGMAX>(t, scores, argmax, dtype, sm_count(), st, variant);
     if (rc == 0) return launch_check("fwd_tc05_kernel");
     if (rc < 0) return fail(MAXSIM_ECUDA, "could not configure the tcgen05 kernel");
     // rc == 1: tensor maps could not be encoded; use the streaming kernel
   }
-  if ((path == 3 || path == 5 || path == 6) && LAYOUT == kContrastive)
+  if ((path == 3 || (path >= 5 && path <= 7)) && LAYOUT == kContrastive)
     return fail(MAXSIM_EUNSUPPORTED, "tcgen05 kernel forced but shape not eligible");
 
   if (path != 1 && mma_eligible(t, dtype)) {

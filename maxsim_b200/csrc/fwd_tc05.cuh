@@ -23,8 +23,13 @@
 //   * the epilogue, not the tensor pipe, sets the pace (with the epilogue
 //     disabled the TMA/MMA pipeline alone runs at 0.92 of the measured bf16
 //     peak), so its arithmetic is arranged for few instructions and much
-//     independent work: 3-input max trees, an argmax search that runs on the
-//     FMA pipe instead of compare/select pairs, a whole tile folded per step.
+//     independent work: 3-input max trees, a whole tile folded per step, and
+//     an argmax search that first picks the 32-column chunk holding the
+//     maximum with selects and then finds the index inside it on the FMA pipe;
+//   * the two producer warps sit in a warpgroup of their own (warps 0-3) that
+//     hands most of its registers to the epilogue warps (setmaxnreg: 40 and
+//     232 per thread), so a whole tile and the fold's temporaries stay in
+//     registers without spills.
 //
 // Every wait is bounded; a wait that runs out records a status bit and the
 // CTA drains to the common exit, where TMEM is released.
@@ -60,7 +65,9 @@ struct Cfg {
   static constexpr int kBN = BN;
   static constexpr int kQPerCta = kQPerSub * MSUB;
   static constexpr int kEpiWarps = 4 * MSUB;
-  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  static constexpr int kProducerWarps = 4;  // TMA, MMA, two idle: a whole warpgroup, so that its
+                                            // registers can be handed to the epilogue warps
+  static constexpr int kThreads = 32 * (kProducerWarps + kEpiWarps);
   static constexpr int kTmemCols = MSUB * BN * kAccStages;
   static constexpr int kBBoxBytes = BN * 128;          // one BN-row x 64-element box
   static constexpr int kBTileBytes = 2 * kBBoxBytes;
@@ -319,6 +326,72 @@ __device__ __forceinline__ void fold128(const float (&a)[32], const float (&b)[3
   }
 }
 
+// The same folds with a cheaper index search.  Once the maximum m of the tile
+// is known, the first 32-column chunk whose own maximum equals m holds the
+// first index; its 32 values are picked per lane with select instructions
+// (one per column for 64 columns, three for 128) and only they go through the
+// FMA-pipe key search: about 1.9 instructions per similarity instead of 3.
+template <bool ARGMAX>
+__device__ __forceinline__ void fold64_sel(const float (&a)[32], const float (&b)[32], int base_ix,
+                                           float& run, int& idx) {
+  const float ma = max32(a);
+  const float m = fmaxf(ma, max32(b));
+  if (ARGMAX) {
+    if (__any_sync(0xffffffffu, m > run)) {
+      const bool in_a = ma == m;
+      float w[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) w[j] = in_a ? a[j] : b[j];
+      int first = first_index_of_max(w, m);
+      if (m > run) {
+        if (first < 0) {  // infinite maximum: compare loop
+          first = 31;
+#pragma unroll
+          for (int j = 30; j >= 0; --j) first = (w[j] == m) ? j : first;
+        }
+        run = m;
+        idx = base_ix + (in_a ? 0 : 32) + first;
+      }
+    }
+  } else {
+    run = fmaxf(run, m);
+  }
+}
+
+template <bool ARGMAX>
+__device__ __forceinline__ void fold128_sel(const float (&a)[32], const float (&b)[32],
+                                            const float (&c)[32], const float (&d)[32],
+                                            int base_ix, float& run, int& idx) {
+  const float ma = max32(a), mb = max32(b), mc = max32(c), md = max32(d);
+  const float mab = fmaxf(ma, mb);
+  const float m = fmaxf(mab, fmaxf(mc, md));
+  if (ARGMAX) {
+    if (__any_sync(0xffffffffu, m > run)) {
+      const bool lower = mab == m;                      // the first maximum lies in a or b
+      const bool even = lower ? (ma == m) : (mc == m);  // ... in the first chunk of that half
+      float w[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float x = lower ? a[j] : c[j];
+        const float y = lower ? b[j] : d[j];
+        w[j] = even ? x : y;
+      }
+      int first = first_index_of_max(w, m);
+      if (m > run) {
+        if (first < 0) {  // infinite maximum: compare loop
+          first = 31;
+#pragma unroll
+          for (int j = 30; j >= 0; --j) first = (w[j] == m) ? j : first;
+        }
+        run = m;
+        idx = base_ix + (lower ? 0 : 64) + (even ? 0 : 32) + first;
+      }
+    }
+  } else {
+    run = fmaxf(run, m);
+  }
+}
+
 // Folds 32 similarities of one document into the row's running maximum and
 // first-index argmax.  `base_ix` is the document-local index of column 0.
 template <bool ARGMAX>
@@ -353,7 +426,10 @@ struct Params {
   uint32_t idesc;
 };
 
-template <bool ARGMAX, int MSUB, int BN>
+// MODE bit 0: select-then-search argmax folds; bit 1: the producer warpgroup
+// gives most of its registers to the epilogue warps (setmaxnreg), which then
+// hold a whole tile plus the fold's temporaries without spilling.
+template <bool ARGMAX, int MSUB, int BN, int MODE = 0>
 __global__ void __launch_bounds__(Cfg<MSUB, BN>::kThreads, Cfg<MSUB, BN>::kMinBlocks)
 fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_d,
                 const Params P) {
@@ -362,6 +438,9 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr int kTmemCols = C::kTmemCols, kQPerCta = C::kQPerCta;
   constexpr size_t kSmemA = C::kSmemA, kSmemB = C::kSmemB;
   (void)kQPerCta;
+  constexpr bool SELECT = (MODE & 1) != 0;
+  constexpr bool REALLOC = (MODE & 2) != 0;
+  static_assert(!REALLOC || (C::kThreads == 384 && C::kMinBlocks == 1), "register hand-over is sized for 12 warps");
   extern __shared__ unsigned char tc05_smem_raw[];
   const uint32_t raw = smem_u32(tc05_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -408,6 +487,8 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // tiles through L2.  (Giving each CTA a contiguous range of items to spare
   // query-block reloads measured slower.)
 
+  if (warp < C::kProducerWarps) {
+  if constexpr (REALLOC) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
   if (warp == 0) {
     // ===================== TMA producer ====================================
     if (lane == 0) {
@@ -473,9 +554,11 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         umma_commit(a_empty);  // query block reusable once this item's MMAs retire
       }
     }
+  }
   } else {
     // ===================== epilogue ========================================
-    const int ew = warp - 2;
+    if constexpr (REALLOC) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
+    const int ew = warp - C::kProducerWarps;
     const int sub = ew >> 2;
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     uint32_t acc = 0, aph = 0;
@@ -572,11 +655,13 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               vd[j] = __uint_as_float(raw[1][32 + j]);
             }
             if (d < d_hi && tok_tile + 128 <= dend) {
-              fold128<ARGMAX>(va, vb, vc, vd, tok_tile - dstart, run, idx);
+              if constexpr (SELECT) fold128_sel<ARGMAX>(va, vb, vc, vd, tok_tile - dstart, run, idx);
+              else fold128<ARGMAX>(va, vb, vc, vd, tok_tile - dstart, run, idx);
               if (tok_tile + 128 == dend) finish_document();
             } else {
               if (d < d_hi && tok_tile + 64 <= dend) {
-                fold64<ARGMAX>(va, vb, tok_tile - dstart, run, idx);
+                if constexpr (SELECT) fold64_sel<ARGMAX>(va, vb, tok_tile - dstart, run, idx);
+                else fold64<ARGMAX>(va, vb, tok_tile - dstart, run, idx);
                 if (tok_tile + 64 == dend) finish_document();
               } else {
                 fold_chunk(va, tok_tile);
@@ -584,7 +669,8 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               }
               if (64 < n_valid) {
                 if (d < d_hi && tok_tile + 128 <= dend) {
-                  fold64<ARGMAX>(vc, vd, tok_tile + 64 - dstart, run, idx);
+                  if constexpr (SELECT) fold64_sel<ARGMAX>(vc, vd, tok_tile + 64 - dstart, run, idx);
+                  else fold64<ARGMAX>(vc, vd, tok_tile + 64 - dstart, run, idx);
                   if (tok_tile + 128 == dend) finish_document();
                 } else {
                   fold_chunk(vc, tok_tile + 64);
@@ -686,7 +772,7 @@ inline bool tc05_eligible(const PairTable& t, int dtype) {
 
 // Returns 0 on success, 1 if the launch could not be prepared (caller falls
 // back to another kernel), or a CUDA error code < 0.
-template <bool ARGMAX, int MSUB, int BN>
+template <bool ARGMAX, int MSUB, int BN, int MODE = 0>
 int launch_tc05_cfg(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
                     cudaStream_t st) {
   using C = tc05::Cfg<MSUB, BN>;
@@ -715,7 +801,7 @@ int launch_tc05_cfg(const PairTable& t, float* scores, int32_t* argmax, int dtyp
   P.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) |
             ((uint32_t)(tc05::kBM >> 4) << 24);
 
-  auto kern = tc05::fwd_tc05_kernel<ARGMAX, MSUB, BN>;
+  auto kern = tc05::fwd_tc05_kernel<ARGMAX, MSUB, BN, MODE>;
   static std::atomic<unsigned char> configured[64];  // same value from every racing thread
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return -3;
@@ -732,15 +818,24 @@ int launch_tc05_cfg(const PairTable& t, float* scores, int32_t* argmax, int dtyp
   return 0;
 }
 
-// variant 0: M = 256, 128-token tiles, one CTA per SM (default)
+// variant 0: M = 256, 128-token tiles, one CTA per SM, the producer warpgroup's
+//            registers handed to the epilogue warps, select-then-search argmax
+//            folds (default)
 // variant 1: M = 512, 64-token tiles, 16 epilogue warps
 // variant 2: M = 256, 64-token tiles, two CTAs per SM
+// variant 3: variant 0 without the register hand-over and with the full-width
+//            argmax search (the earlier epilogue, kept for comparison)
 template <bool ARGMAX>
 int launch_tc05(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
                 cudaStream_t st, int variant) {
   if (variant == 1) return launch_tc05_cfg<ARGMAX, 4, 64>(t, scores, argmax, dtype, sms, st);
   if (variant == 2) return launch_tc05_cfg<ARGMAX, 2, 64>(t, scores, argmax, dtype, sms, st);
-  return launch_tc05_cfg<ARGMAX, 2, 128>(t, scores, argmax, dtype, sms, st);
+  if constexpr (ARGMAX) {
+    if (variant == 3) return launch_tc05_cfg<true, 2, 128, 0>(t, scores, argmax, dtype, sms, st);
+    return launch_tc05_cfg<true, 2, 128, 3>(t, scores, argmax, dtype, sms, st);
+  } else {
+    return launch_tc05_cfg<false, 2, 128, 2>(t, scores, argmax, dtype, sms, st);
+  }
 }
 
 }  // namespace maxsim

@@ -56,7 +56,9 @@ SHAPES = [
 
 @pytest.mark.parametrize("Nq,d_lens", SHAPES)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-@pytest.mark.parametrize("path", [3, 5, 6])  # 3: default, 5: M = 512 / 64-token tiles, 6: two CTAs per SM
+# 3: default, 5: M = 512 / 64-token tiles, 6: two CTAs per SM, 7: the earlier epilogue (no
+# register hand-over, full-width argmax search)
+@pytest.mark.parametrize("path", [3, 5, 6, 7])
 def test_tc05_matches_oracle(Nq, d_lens, dtype, path):
     _ops.set_forward_path(path)
     q, d, off = _make(Nq, d_lens, dtype, 11)
@@ -73,7 +75,9 @@ def test_tc05_agrees_with_streaming_kernel_bitwise_on_argmax():
     assert (a_tc != a_mma).float().mean() < 1e-3
 
 
-def test_tc05_exact_ties_and_duplicated_tokens():
+@pytest.mark.parametrize("path", [3, 7])
+def test_tc05_exact_ties_and_duplicated_tokens(path):
+    _ops.set_forward_path(path)
     wl = W.c5_contrastive_ties_bf16(seed=21, Nq=16, Nb=24, lo=20, hi=300, dup_frac=0.1)
     q = W.to_torch(wl.queries, "bf16", DEV)
     d = W.to_torch(wl.documents, "bf16", DEV)
@@ -94,7 +98,9 @@ def test_tc05_exact_ties_and_duplicated_tokens():
     assert (a2 == 0).all()
 
 
-def test_tc05_non_finite_contract():
+@pytest.mark.parametrize("path", [3, 7])
+def test_tc05_non_finite_contract(path):
+    _ops.set_forward_path(path)
     q, d, off = _make(16, [64, 200, 33], torch.float16, 13)
     q[3, 5, 7] = float("nan")
     d[70, 1] = float("nan")
