@@ -70,9 +70,12 @@ MAXSIM_API int maxsim_b200_device_status(void* stream);
 MAXSIM_API int64_t maxsim_b200_launch_count(void);
 /* Selects the forward implementation: 0 = automatic, 1 = force the portable
  * SIMT kernel, 2 = force the warp-MMA streaming kernel where eligible,
- * 3 = force the tcgen05 kernel where eligible, 5 / 6 = force its alternative
- * configurations (M = 512 with 64-token tiles / two CTAs per SM).  For tests
- * and profiling. */
+ * 3 = force the tcgen05 kernels where eligible, 5 / 6 = force their alternative
+ * configurations (M = 512 with 64-token tiles / two CTAs per SM), 7 = the
+ * earlier epilogue (no register hand-over, full-width argmax search),
+ * 8 = tiles that start at document starts, 9 = tiles that ignore document
+ * boundaries (0 and 3 choose between 8 and 9 by average document length).
+ * For tests and profiling. */
 MAXSIM_API void maxsim_b200_set_forward_path(int path);
 
 /* Host-side validation helper (no reference counterpart: the reference copies

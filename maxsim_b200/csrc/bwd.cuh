@@ -235,6 +235,24 @@ bwd_dq_gather16_kernel(PairTable t, const float* __restrict__ dscore,
         }
       }
       const int n = min(32, C - c0);
+      if (n == 32 && k_ok && __all_sync(0xffffffffu, src >= 0)) {
+        // all 32 candidates routed (the usual case): no per-row checks
+#pragma unroll 1
+        for (int l0 = 0; l0 < 32; l0 += 8) {
+          Row8<T> rows[4];
+          float gw[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int l = l0 + 2 * u + half;
+            gw[u] = __shfl_sync(0xffffffffu, gl, l);
+            const int32_t sr = __shfl_sync(0xffffffffu, src, l);
+            rows[u].load(D + (int64_t)sr * dim + k);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) rows[u].fma_into(gw[u], acc);
+        }
+        continue;
+      }
       for (int l0 = 0; l0 < n; l0 += 8) {
         Row8<T> rows[4];
         float gw[4];

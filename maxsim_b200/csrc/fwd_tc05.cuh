@@ -611,21 +611,24 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             // Columns of this chunk that belong to document d: [col, seg_end).
             if (col == 0 && seg_end == 32) {
               fold32<ARGMAX>(v, base_ix, run, idx);
-            } else if (ARGMAX) {
-              // boundary chunk: per-column predicated update (fewest instructions)
+            } else {
+              // boundary chunk: per-column predicated update; groups of eight
+              // columns that lie outside the document are skipped (warp-uniform)
 #pragma unroll
-              for (int j = 0; j < 32; ++j) {
-                if (j >= col && j < seg_end) {
-                  if (v[j] > run) { run = v[j]; idx = base_ix + j; }
+              for (int g8 = 0; g8 < 32; g8 += 8) {
+                if (g8 + 8 > col && g8 < seg_end) {
+#pragma unroll
+                  for (int j = g8; j < g8 + 8; ++j) {
+                    if (j >= col && j < seg_end) {
+                      if (ARGMAX) {
+                        if (v[j] > run) { run = v[j]; idx = base_ix + j; }
+                      } else {
+                        run = fmaxf(run, v[j]);
+                      }
+                    }
+                  }
                 }
               }
-            } else {
-              float w[32];
-              const unsigned span = (unsigned)(seg_end - col);
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                w[j] = ((unsigned)(j - col) < span) ? v[j] : neg_inf();
-              fold32<false>(w, base_ix, run, idx);
             }
             col = max(col, seg_end);
             if (tok0 + col >= dend) finish_document();

@@ -57,8 +57,9 @@ SHAPES = [
 @pytest.mark.parametrize("Nq,d_lens", SHAPES)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 # 3: default, 5: M = 512 / 64-token tiles, 6: two CTAs per SM, 7: the earlier epilogue (no
-# register hand-over, full-width argmax search)
-@pytest.mark.parametrize("path", [3, 5, 6, 7])
+# register hand-over, full-width argmax search), 8: tiles that start at document starts,
+# 9: tiles that ignore document boundaries (3 chooses between 8 and 9 by document length)
+@pytest.mark.parametrize("path", [3, 5, 6, 7, 8, 9])
 def test_tc05_matches_oracle(Nq, d_lens, dtype, path):
     _ops.set_forward_path(path)
     q, d, off = _make(Nq, d_lens, dtype, 11)
@@ -75,7 +76,7 @@ def test_tc05_agrees_with_streaming_kernel_bitwise_on_argmax():
     assert (a_tc != a_mma).float().mean() < 1e-3
 
 
-@pytest.mark.parametrize("path", [3, 7])
+@pytest.mark.parametrize("path", [7, 8, 9])
 def test_tc05_exact_ties_and_duplicated_tokens(path):
     _ops.set_forward_path(path)
     wl = W.c5_contrastive_ties_bf16(seed=21, Nq=16, Nb=24, lo=20, hi=300, dup_frac=0.1)
@@ -98,7 +99,7 @@ def test_tc05_exact_ties_and_duplicated_tokens(path):
     assert (a2 == 0).all()
 
 
-@pytest.mark.parametrize("path", [3, 7])
+@pytest.mark.parametrize("path", [7, 8, 9])
 def test_tc05_non_finite_contract(path):
     _ops.set_forward_path(path)
     q, d, off = _make(16, [64, 200, 33], torch.float16, 13)
