@@ -652,17 +652,21 @@ bwd_route_atomic_kernel(PairTable t, const float* __restrict__ dscore,
 // documents longer than kInvBins tokens in token chunks; later passes add to
 // the rows the first pass stored.
 // ---------------------------------------------------------------------------
+// Sized for two CTAs per SM (88 KB of shared memory and at most 64 registers
+// per thread), so that one document's histogram / scan / scatter phases, which
+// wait on memory and barriers, overlap the other's gather.
 constexpr int kInvThreads = 512;
-constexpr int kInvEntries = 32768;  // entry ids held per pass (128 KB)
+constexpr int kInvEntries = 32768;  // entry ids held per pass (16-bit ids: 64 KB)
 constexpr int kInvBins = 2048;      // document tokens per chunk
-constexpr int kInvMaxQ = 4096;      // queries per pass (g column held in shared memory)
+constexpr int kInvMaxQ = 2048;      // queries per pass (g column held in shared memory)
 
 constexpr size_t inv_smem_bytes() {
-  return (size_t)kInvEntries * 4 + (size_t)kInvMaxQ * 4 + (size_t)(2 * kInvBins + 2) * 4 + 16;
+  return (size_t)kInvEntries * 2 + (size_t)kInvMaxQ * 4 + (size_t)(2 * kInvBins + 2) * 4 + 16;
 }
+static_assert(kInvEntries <= 65536, "entry ids are stored in 16 bits");
 
 template <typename T>
-__global__ void __launch_bounds__(kInvThreads, 1)
+__global__ void __launch_bounds__(kInvThreads, 2)
 bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
                      const int32_t* __restrict__ argmax, void* __restrict__ dd_out, int Nq,
                      int native) {
@@ -670,7 +674,7 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
   // entries of a document fit one pass; the fp32 form adds later passes in place.
   float* dd = reinterpret_cast<float*>(dd_out);
   extern __shared__ __align__(16) unsigned char inv_smem[];
-  int32_t* list = reinterpret_cast<int32_t*>(inv_smem);                 // [kInvEntries]
+  uint16_t* list = reinterpret_cast<uint16_t*>(inv_smem);               // [kInvEntries]
   float* gcol = reinterpret_cast<float*>(list + kInvEntries);          // [kInvMaxQ]
   int32_t* bin_start = reinterpret_cast<int32_t*>(gcol + kInvMaxQ);    // [kInvBins + 1]
   int32_t* cursor = bin_start + kInvBins + 1;                          // [kInvBins]
@@ -751,7 +755,8 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u)
-          if (a[u] >= 0 && a[u] < ntok) list[atomicAdd(&cursor[a[u]], 1)] = e0 + u * kInvThreads;
+          if (a[u] >= 0 && a[u] < ntok)
+            list[atomicAdd(&cursor[a[u]], 1)] = (uint16_t)(e0 + u * kInvThreads);
       }
       __syncthreads();
       // gather: warps claim tokens; each half-warp fetches one routed query row
@@ -771,7 +776,7 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
           float acc[8];
 #pragma unroll
           for (int x = 0; x < 8; ++x) acc[x] = 0.f;
-          constexpr int kFlight = sizeof(T) == 2 ? 8 : 4;  // rows in flight per lane
+          constexpr int kFlight = sizeof(T) == 2 ? 4 : 2;  // rows in flight per lane
           int p = beg + half;
           if (k_ok) {
             // full groups: no bounds checks
@@ -787,13 +792,20 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
 #pragma unroll
               for (int u = 0; u < kFlight; ++u) rows[u].fma_into(gw[u], acc);
             }
-            // tail
-            for (; p < end; p += 2) {
-              const int e = list[p];
-              const float g1 = gcol[lq_shift >= 0 ? (e >> lq_shift) : (e / Lq)];
-              Row8<T> r;
-              r.load(qk + (int64_t)e * dim);
-              r.fma_into(g1, acc);
+            // tail: one more group with its loads issued together, absent rows weighted 0
+            if (p < end) {
+              Row8<T> rows[kFlight];
+              float gw[kFlight];
+#pragma unroll
+              for (int u = 0; u < kFlight; ++u) {
+                const bool has = p + 2 * u < end;
+                const int e = has ? list[p + 2 * u] : 0;
+                gw[u] = has ? gcol[lq_shift >= 0 ? (e >> lq_shift) : (e / Lq)] : 0.f;
+                rows[u].zero();
+                if (has) rows[u].load(qk + (int64_t)e * dim);
+              }
+#pragma unroll
+              for (int u = 0; u < kFlight; ++u) rows[u].fma_into(gw[u], acc);
             }
           }
 #pragma unroll
