@@ -139,7 +139,9 @@ def test_pack_is_differentiable_and_feeds_the_contrastive_operator():
 
     assert torch.equal(docs, docs2)
     torch.testing.assert_close(loss1, loss2, rtol=0, atol=0)
-    assert torch.equal(e1.grad, e2.grad)
+    # grad_documents sums a token's routed query rows in the order shared-memory atomics
+    # set, which varies between launches: equal up to the last place of bf16
+    torch.testing.assert_close(e1.grad.float(), e2.grad.float(), rtol=2.0 ** -6, atol=1e-4)
     mask = (torch.arange(L)[None, :] < lengths[:, None]).to(DEV)
     assert bool((e1.grad[~mask] == 0).all())
     assert float(e1.grad.float().abs().sum()) > 0
