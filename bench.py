@@ -632,7 +632,9 @@ def run_contrastive_profile(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     n = 512 if args.small else 1024
-    data = W.c5_device(dev, Nq=n, Nb=n)
+    # --short-docs: 32-256 tokens per document, the range served by the kernel
+    # whose tiles start at document starts
+    data = W.c5_device(dev, Nq=n, Nb=n, lo=32, hi=256) if args.short_docs else W.c5_device(dev, Nq=n, Nb=n)
     q = data["queries"].requires_grad_(True)
     d = data["documents"].requires_grad_(True)
     off = data["document_offsets"]
@@ -902,6 +904,8 @@ def main():
     ap.add_argument("--profile-contrastive", action="store_true",
                     help="run only contrastive forward+backward steps of the ties configuration "
                          "(Nq=Nb=1024, or 512 with --small); for profiler captures")
+    ap.add_argument("--short-docs", action="store_true",
+                    help="with --profile-contrastive: documents of 32-256 tokens instead of 64-512")
     ap.add_argument("--profile-packed", action="store_true",
                     help="run only train steps of the packed pair grid (65536 pairs); for profiler captures")
     ap.add_argument("--list-order", action="store_true",
