@@ -259,12 +259,10 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
         constexpr size_t smem = inv_smem_bytes();
         static std::atomic<unsigned char> configured[kMaxDevices];
         if (int rc = ensure_smem(kern, smem, configured)) return rc;
-        // One CTA per document.  Documents longer than kInvBins tokens are
-        // covered by the kernel's stride over token chunks; a second CTA row
-        // helps only when the mean document is that long.
-        const int gy = (d_rows / Nb > kInvBins) ? 2 : 1;
+        int gy, split;
+        inv_grid_shape(Nb, d_rows / Nb, sm_count(), &gy, &split);
         dim3 grid((unsigned)Nb, (unsigned)gy);
-        kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 0);
+        kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 0, split);
         return launch_check("bwd_dd_invert_kernel");
       }
       MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
@@ -338,9 +336,10 @@ int run_backward_native_t(const PairTable& t, const float* dscore, const int32_t
     constexpr size_t smem = inv_smem_bytes();
     static std::atomic<unsigned char> configured[kMaxDevices];
     if (int rc = ensure_smem(kern, smem, configured)) return rc;
-    const int gy = (d_rows / Nb > kInvBins) ? 2 : 1;
+    int gy, split;
+    inv_grid_shape(Nb, d_rows / Nb, sm_count(), &gy, &split);
     dim3 grid((unsigned)Nb, (unsigned)gy);
-    kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 1);
+    kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 1, split);
     return launch_check("bwd_dd_invert_kernel");
   }
 }

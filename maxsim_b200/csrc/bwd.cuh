@@ -665,11 +665,31 @@ constexpr size_t inv_smem_bytes() {
 }
 static_assert(kInvEntries <= 65536, "entry ids are stored in 16 bits");
 
+// Grid rows per document for `documents` documents of `mean_tokens` tokens on
+// `sms` SMs (two CTAs each).  With at least half as many documents as CTA slots:
+// one CTA per document (two for very long documents), chunks of kInvBins tokens.
+// With fewer: up to eight CTAs per document, each taking an even share of its
+// tokens (*split = 1).
+inline void inv_grid_shape(int64_t documents, int64_t mean_tokens, int sms, int* gy, int* split) {
+  const int64_t slots = 2ll * sms;
+  *gy = mean_tokens > kInvBins ? 2 : 1;
+  *split = 0;
+  if (documents > 0 && documents * 2 <= slots && mean_tokens <= kInvBins) {
+    int64_t rows = slots / documents;
+    if (rows > 8) rows = 8;
+    *gy = (int)rows;
+    *split = 1;
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kInvThreads, 2)
 bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
                      const int32_t* __restrict__ argmax, void* __restrict__ dd_out, int Nq,
-                     int native) {
+                     int native, int split) {
+  // CTA (d, y) takes the token chunks y, y + gridDim.y, ... of document d.  A chunk
+  // is kInvBins tokens, or, with `split` set (few documents, several CTAs per
+  // document), an even share of the document.
   // `native` (rows stored once, in the inputs' type) is only given when all
   // entries of a document fit one pass; the fp32 form adds later passes in place.
   float* dd = reinterpret_cast<float*>(dd_out);
@@ -691,8 +711,9 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
   if (q_block > kInvMaxQ) q_block = kInvMaxQ;
   if (q_block < 1) q_block = 1;  // the dispatcher guarantees Lq <= kInvEntries
 
-  for (int tok0 = blockIdx.y * kInvBins; tok0 < Ld; tok0 += gridDim.y * kInvBins) {
-    const int ntok = min(kInvBins, Ld - tok0);
+  const int bins = split ? min(kInvBins, (Ld + (int)gridDim.y - 1) / (int)gridDim.y) : kInvBins;
+  for (int tok0 = blockIdx.y * bins; tok0 < Ld; tok0 += gridDim.y * bins) {
+    const int ntok = min(bins, Ld - tok0);
     for (int q0 = 0; q0 < Nq; q0 += q_block) {
       const int nq = min(q_block, Nq - q0);
       const int n_e = nq * Lq;
