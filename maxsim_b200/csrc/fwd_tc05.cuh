@@ -773,50 +773,67 @@ inline bool tc05_eligible(const PairTable& t, int dtype) {
   return tensor_map_encoder() != nullptr;
 }
 
+// Work partition and instruction descriptor of a launch whose CTAs take
+// `q_per_cta` queries and document tiles of `bn` tokens.  False if the item
+// count does not fit 32 bits.
+inline bool tc05_fill_params(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
+                             int q_per_cta, int bn, tc05::Params* P) {
+  const int64_t Nb = t.C, Nq = t.n_pairs / Nb;
+  P->doc_offsets = t.ib;
+  P->scores = scores;
+  P->argmax = argmax;
+  P->Nq = (int32_t)Nq;
+  P->Nb = (int32_t)Nb;
+  P->n_qgroups = (int32_t)((Nq + q_per_cta - 1) / q_per_cta);
+  int64_t dpi = (Nb * (int64_t)P->n_qgroups) / (16ll * sms);
+  if (dpi < 1) dpi = 1;
+  if (dpi > Nb) dpi = Nb;
+  P->docs_per_item = (int32_t)dpi;
+  const int64_t n_dc = (Nb + dpi - 1) / dpi;
+  const int64_t n_items = n_dc * P->n_qgroups;
+  if (n_items >= (1ll << 31)) return false;
+  P->n_items = (int32_t)n_items;
+  const uint32_t fmt = dtype == 2 ? 1u : 0u;  // bf16 : fp16
+  P->idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) |
+             ((uint32_t)(tc05::kBM >> 4) << 24);
+  return true;
+}
+
+// Opt `kern` in to `smem` bytes of dynamic shared memory once per device.
+// `configured` is the kernel's own flag array (one per instantiation).
+template <typename Kernel>
+int tc05_configure(Kernel kern, size_t smem, std::atomic<unsigned char> (&configured)[64]) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -3;
+  const bool track = dev >= 0 && dev < 64;
+  if (!track || !configured[dev].load(std::memory_order_acquire)) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) !=
+        cudaSuccess)
+      return -3;
+    if (track) configured[dev].store(1, std::memory_order_release);  // same value from every racing thread
+  }
+  return 0;
+}
+
 // Returns 0 on success, 1 if the launch could not be prepared (caller falls
 // back to another kernel), or a CUDA error code < 0.
 template <bool ARGMAX, int MSUB, int BN, int MODE = 0>
 int launch_tc05_cfg(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
                     cudaStream_t st) {
   using C = tc05::Cfg<MSUB, BN>;
-  const int64_t Nb = t.C, Nq = t.n_pairs / Nb;
+  const int64_t Nq = t.n_pairs / t.C;
   CUtensorMap tm_q, tm_d;
   const bool bf16 = dtype == 2;
   if (!encode_rows128(&tm_q, t.queries, Nq * tc05::kLq, tc05::kBM, bf16)) return 1;
   if (!encode_rows128(&tm_d, t.documents, t.d_rows, BN, bf16)) return 1;
-
   tc05::Params P;
-  P.doc_offsets = t.ib;
-  P.scores = scores;
-  P.argmax = argmax;
-  P.Nq = (int32_t)Nq;
-  P.Nb = (int32_t)Nb;
-  P.n_qgroups = (int32_t)((Nq + C::kQPerCta - 1) / C::kQPerCta);
-  int64_t dpi = (Nb * (int64_t)P.n_qgroups) / (16ll * sms);
-  if (dpi < 1) dpi = 1;
-  if (dpi > Nb) dpi = Nb;
-  P.docs_per_item = (int32_t)dpi;
-  const int64_t n_dc = (Nb + dpi - 1) / dpi;
-  const int64_t n_items = n_dc * P.n_qgroups;
-  if (n_items >= (1ll << 31)) return 1;
-  P.n_items = (int32_t)n_items;
-  const uint32_t fmt = bf16 ? 1u : 0u;
-  P.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(BN >> 3) << 17) |
-            ((uint32_t)(tc05::kBM >> 4) << 24);
+  if (!tc05_fill_params(t, scores, argmax, dtype, sms, C::kQPerCta, BN, &P)) return 1;
 
   auto kern = tc05::fwd_tc05_kernel<ARGMAX, MSUB, BN, MODE>;
-  static std::atomic<unsigned char> configured[64];  // same value from every racing thread
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return -3;
-  const bool track = dev >= 0 && dev < 64;
-  if (!track || !configured[dev].load(std::memory_order_acquire)) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)C::kSmemBytes) != cudaSuccess)
-      return -3;
-    if (track) configured[dev].store(1, std::memory_order_release);
-  }
+  static std::atomic<unsigned char> configured[64];
+  if (int rc = tc05_configure(kern, C::kSmemBytes, configured)) return rc;
   const int64_t slots = (int64_t)sms * C::kMinBlocks;
-  const int grid = (int)(n_items < slots ? n_items : slots);
+  const int grid = (int)(P.n_items < slots ? P.n_items : slots);
   kern<<<grid, C::kThreads, C::kSmemBytes, st>>>(tm_q, tm_d, P);
   return 0;
 }

@@ -291,45 +291,19 @@ template <bool ARGMAX>
 int launch_tc05_doc(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
                     cudaStream_t st) {
   using C = tc05::Cfg<2, 128>;
-  const int64_t Nb = t.C, Nq = t.n_pairs / Nb;
-  CUtensorMap tm_q, tm_d;
+  const int64_t Nq = t.n_pairs / t.C;
+  CUtensorMap tm_q, tm_d, tm_d32;
   const bool bf16 = dtype == 2;
   if (!encode_rows128(&tm_q, t.queries, Nq * tc05::kLq, tc05::kBM, bf16)) return 1;
   if (!encode_rows128(&tm_d, t.documents, t.d_rows, C::kBN, bf16)) return 1;
-  CUtensorMap tm_d32;
   if (!encode_rows128(&tm_d32, t.documents, t.d_rows, 32, bf16)) return 1;
-
   tc05::Params P;
-  P.doc_offsets = t.ib;
-  P.scores = scores;
-  P.argmax = argmax;
-  P.Nq = (int32_t)Nq;
-  P.Nb = (int32_t)Nb;
-  P.n_qgroups = (int32_t)((Nq + C::kQPerCta - 1) / C::kQPerCta);
-  int64_t dpi = (Nb * (int64_t)P.n_qgroups) / (16ll * sms);
-  if (dpi < 1) dpi = 1;
-  if (dpi > Nb) dpi = Nb;
-  P.docs_per_item = (int32_t)dpi;
-  const int64_t n_dc = (Nb + dpi - 1) / dpi;
-  const int64_t n_items = n_dc * P.n_qgroups;
-  if (n_items >= (1ll << 31)) return 1;
-  P.n_items = (int32_t)n_items;
-  const uint32_t fmt = bf16 ? 1u : 0u;
-  P.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(C::kBN >> 3) << 17) |
-            ((uint32_t)(tc05::kBM >> 4) << 24);
+  if (!tc05_fill_params(t, scores, argmax, dtype, sms, C::kQPerCta, C::kBN, &P)) return 1;
 
   auto kern = tc05::fwd_tc05_doc_kernel<ARGMAX>;
-  static std::atomic<unsigned char> configured[64];  // same value from every racing thread
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return -3;
-  const bool track = dev >= 0 && dev < 64;
-  if (!track || !configured[dev].load(std::memory_order_acquire)) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             (int)C::kSmemBytes) != cudaSuccess)
-      return -3;
-    if (track) configured[dev].store(1, std::memory_order_release);
-  }
-  const int grid = (int)(n_items < sms ? n_items : sms);
+  static std::atomic<unsigned char> configured[64];
+  if (int rc = tc05_configure(kern, C::kSmemBytes, configured)) return rc;
+  const int grid = (int)(P.n_items < sms ? P.n_items : sms);
   kern<<<grid, C::kThreads, C::kSmemBytes, st>>>(tm_q, tm_d, tm_d32, P);
   return 0;
 }
