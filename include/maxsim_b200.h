@@ -70,12 +70,11 @@ MAXSIM_API int maxsim_b200_device_status(void* stream);
 MAXSIM_API int64_t maxsim_b200_launch_count(void);
 /* Selects the forward implementation: 0 = automatic, 1 = force the portable
  * SIMT kernel, 2 = force the warp-MMA streaming kernel where eligible,
- * 3 = force the tcgen05 kernels where eligible, 5 / 6 = force their alternative
- * configurations (M = 512 with 64-token tiles / two CTAs per SM), 7 = the
- * earlier epilogue (no register hand-over, full-width argmax search),
- * 8 = tiles that start at document starts, 9 = tiles that ignore document
- * boundaries (0 and 3 choose between 8 and 9 by average document length).
- * For tests and profiling. */
+ * 3 = the contrastive operators fail instead of leaving the tcgen05 kernel,
+ * 8 = as 3 with every document tiled on its own, 9 = as 3 with 128-token tiles
+ * that ignore document boundaries (0 and 3 choose between 8 and 9 by average
+ * document length).  A process-wide switch for tests and profiling: do not
+ * change it while another thread is calling an operator. */
 MAXSIM_API void maxsim_b200_set_forward_path(int path);
 
 /* Host-side validation helper (no reference counterpart: the reference copies
@@ -310,6 +309,46 @@ MAXSIM_API int maxsim_contrastive_forward_with_argmax(
     float* scores, int32_t* argmax,
     int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim,
     int64_t total_d_tokens, int dtype, void* stream);
+
+/* Column block of a score matrix (no reference counterpart: the reference has
+ * no multi-device code; this is what the sharded training driver is built
+ * from).  As maxsim_contrastive_forward_with_argmax for the Nb documents
+ * described by document_offsets [Nb+1] (absolute token rows of `documents`,
+ * which has total_d_tokens rows), except that pair (q, d) is written to slot
+ * q * out_ld + out_col0 + d of scores [Nq, out_ld] / argmax [Nq, out_ld, Lq]:
+ * launches over different document ranges, or different document tensors,
+ * fill one matrix.  block_tokens: tokens in the block if known, else 0 (steers
+ * the choice of tiling only).  MAXSIM_EUNSUPPORTED, with nothing written, for
+ * shapes outside the tcgen05 kernel (float16 / bfloat16, Lq <= 64, dim a
+ * multiple of 16 up to 128, at least 2 * 128 / lanes-per-query queries). */
+MAXSIM_API int maxsim_contrastive_forward_with_argmax_block(
+    const void* queries, const void* documents, const int32_t* document_offsets,
+    float* scores, int32_t* argmax,
+    int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim, int64_t total_d_tokens,
+    int64_t block_tokens, int64_t out_ld, int64_t out_col0, int dtype, void* stream);
+
+/* Sharded training, owner exchange (no reference counterpart).
+ * pack_owner_records regroups the pairs of a rank's queries by the rank that
+ * owns the document: argmax [Nq, Nb, Lq] and dscore [Nq, Nb] become one int32
+ * buffer `send` of Nq * Nb * (Lq + 1) words in which owner o's block
+ * [Nq, n_o, Lq + 1] -- the Lq winning tokens of each pair, then the bits of
+ * its score gradient -- starts at word col_start[o] * Nq * (Lq + 1);
+ * col_start [n_owners + 1] (device) holds every owner's first column.
+ * backward_documents_from_records computes grad_documents [total_d_tokens,
+ * dim] of a rank's own documents from records [Nq, Nb, Lq + 1] (the blocks of
+ * all ranks' queries, concatenated in rank order) and all queries
+ * [Nq, Lq, dim]; native != 0 writes the gradient in the inputs' 16-bit type
+ * (needs Nq * Lq <= 32768, dim <= 128), else float.  MAXSIM_EUNSUPPORTED for
+ * shapes the routing kernel does not cover (dim % 8 != 0, misaligned). */
+MAXSIM_API int maxsim_b200_pack_owner_records(const int32_t* argmax, const float* dscore,
+                                              const int32_t* col_start, int64_t n_owners,
+                                              int64_t Nq, int64_t Nb, int64_t Lq,
+                                              int32_t* send, void* stream);
+MAXSIM_API int maxsim_contrastive_backward_documents_from_records(
+    const int32_t* records, const void* queries, const void* documents,
+    const int32_t* document_offsets, void* grad_documents,
+    int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim, int64_t total_d_tokens,
+    int dtype, int native, void* stream);
 
 /* Replaces maxsim_contrastive_backward (maxsim_cuda/maxsim.cu:1856-1920).
  * dscore [Nq, Nb]; grad_queries [Nq, Lq, dim], grad_documents

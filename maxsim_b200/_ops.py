@@ -61,6 +61,9 @@ _SIGNATURES = {
     "maxsim_contrastive_forward": (c_int, [_P] * 4 + [_I64] * 5 + [c_int, _P]),
     "maxsim_contrastive_forward_with_argmax": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, _P]),
     "maxsim_contrastive_backward": (c_int, [_P] * 7 + [_I64] * 5 + [c_int, _P]),
+    "maxsim_contrastive_forward_with_argmax_block": (c_int, [_P] * 5 + [_I64] * 8 + [c_int, _P]),
+    "maxsim_b200_pack_owner_records": (c_int, [_P] * 3 + [_I64] * 4 + [_P, _P]),
+    "maxsim_contrastive_backward_documents_from_records": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, c_int, _P]),
     "maxsim_padded_backward_native": (c_int, [_P] * 8 + [_I64] * 5 + [c_int, _P]),
     "maxsim_contrastive_backward_native": (c_int, [_P] * 7 + [_I64] * 5 + [c_int, _P]),
 }
@@ -86,6 +89,8 @@ def load_library() -> ctypes.CDLL:
                 ) from exc
     lib = ctypes.CDLL(str(path))
     for name, (restype, argtypes) in _SIGNATURES.items():
+        if override and not hasattr(lib, name):
+            continue  # an older build, loaded for comparison, may lack newer entry points
         fn = getattr(lib, name)
         fn.restype = restype
         fn.argtypes = argtypes
@@ -366,9 +371,18 @@ def _groups(key: torch.Tensor, ids32: torch.Tensor, n_bins: int, build: bool = T
     """``(order, ends)`` of a pair-id tensor, or None.  ``key`` is the tensor
     object the caller passed: its grouping is remembered until the tensor is
     written to or dies.  With ``build=False`` only a remembered grouping is
-    returned."""
+    returned.
+
+    The memory trusts torch's version counter: a write that does not bump it
+    (``tensor.data``, a DLPack / external-library view of the same storage)
+    leaves a stale grouping behind; call :func:`forget_pair_groups` after such
+    a write.  While a CUDA graph is being captured nothing is remembered or
+    looked up: the grouping kernels are launched into the capture, so that a
+    replay groups the pair ids that are in the tensors at replay time."""
     if not _group_enabled or ids32.shape[0] < GROUP_MIN_PAIRS or n_bins <= 0:
         return None
+    if torch.cuda.is_current_stream_capturing():
+        return group_pairs(ids32, n_bins) if build else None
     ent = _GROUP_CACHE.get(id(key))
     if ent is not None and ent[0]() is key and ent[1] == key._version and ent[2] == n_bins:
         return ent[3]
@@ -382,6 +396,11 @@ def _groups(key: torch.Tensor, ids32: torch.Tensor, n_bins: int, build: bool = T
     except TypeError:
         pass
     return groups
+
+
+def forget_pair_groups() -> None:
+    """Drop every remembered grouping of a pair-id tensor."""
+    _GROUP_CACHE.clear()
 
 
 def _packed_args(queries, query_offsets, documents, document_offsets,
@@ -604,9 +623,11 @@ def padded_backward_native(dscore, queries, documents, query_lengths, doc_length
     return dq, dd
 
 
-def contrastive_backward_native(dscore, queries, documents, document_offsets, argmax):
+def contrastive_backward_native(dscore, queries, documents, document_offsets, argmax,
+                                want_documents: bool = True):
     """As ``maxsim_contrastive_backward`` with gradients in the inputs' 16-bit
-    type; None when the shape is not covered."""
+    type; None when the shape is not covered.  With ``want_documents=False``
+    only grad_queries is computed (the second entry of the pair is None)."""
     if not _native_grads or queries.dtype not in (torch.float16, torch.bfloat16):
         return None
     dev = _require_cuda(queries, dscore, documents, document_offsets, argmax)
@@ -616,10 +637,10 @@ def contrastive_backward_native(dscore, queries, documents, document_offsets, ar
     if tuple(g.shape) != (Nq, Nb) or tuple(a.shape) != (Nq, Nb, Lq) or Nq * Nb == 0:
         return None
     dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
-    dd = torch.empty(d.shape, dtype=d.dtype, device=dev)
+    dd = torch.empty(d.shape, dtype=d.dtype, device=dev) if want_documents else None
     with _on_device(dev):
         rc = load_library().maxsim_contrastive_backward_native(
-            _ptr(g), _ptr(q), _ptr(d), _ptr(off), _ptr(a), _ptr(dq), _ptr(dd),
+            _ptr(g), _ptr(q), _ptr(d), _ptr(off), _ptr(a), _ptr(dq), _ptr(dd) if dd is not None else 0,
             Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
     if rc == _EUNSUPPORTED:
         return None
@@ -682,6 +703,81 @@ def maxsim_contrastive_forward_with_argmax(queries, documents, document_offsets)
             Nq, Lq, Nb, dim, d.shape[0], _code(q), _stream_ptr())
     _check(rc, "maxsim_contrastive_forward_with_argmax")
     return scores, argmax
+
+
+def contrastive_forward_block(queries, documents, block_offsets, scores, argmax, col0: int,
+                              block_tokens: int = 0) -> bool:
+    """Scores ``queries [Nq, Lq, D]`` against the documents described by
+    ``block_offsets [n + 1]`` (absolute token rows of the packed ``documents``)
+    and writes them into columns ``[col0, col0 + n)`` of the caller's
+    ``scores [Nq, Nb_total]`` fp32 and ``argmax [Nq, Nb_total, Lq]`` int32: several
+    launches over different document ranges (or different ``documents``
+    tensors) fill one score matrix.  ``block_tokens`` is the number of tokens
+    in the block when known (it steers the choice of tiling).  Returns False
+    when the shape is outside what the tcgen05 kernel covers (nothing was
+    written); the caller then scores the block on its own and copies."""
+    dev = _require_cuda(queries, documents, block_offsets, scores, argmax)
+    q, d, off, Nq, Lq, n, dim = _contrastive_args(queries, documents, block_offsets)
+    if scores.dtype != torch.float32 or argmax.dtype != torch.int32 or not scores.is_contiguous() \
+            or not argmax.is_contiguous() or scores.dim() != 2 or scores.shape[0] != Nq \
+            or tuple(argmax.shape) != (Nq, scores.shape[1], Lq):
+        raise RuntimeError("scores must be contiguous [Nq, Nb_total] float32 and argmax [Nq, Nb_total, Lq] int32")
+    if Nq * n == 0:
+        return True
+    with _on_device(dev):
+        rc = load_library().maxsim_contrastive_forward_with_argmax_block(
+            _ptr(q), _ptr(d), _ptr(off), scores.data_ptr(), argmax.data_ptr(),
+            Nq, Lq, n, dim, d.shape[0], int(block_tokens), scores.shape[1], int(col0), _code(q),
+            _stream_ptr())
+    if rc == _EUNSUPPORTED:
+        return False
+    _check(rc, "maxsim_contrastive_forward_with_argmax_block")
+    return True
+
+
+def pack_owner_records(argmax, dscore, col_start) -> torch.Tensor:
+    """Regroups the pairs of this rank's queries by the rank that owns the
+    document: ``argmax [Nq, Nb, Lq]`` int32 and ``dscore [Nq, Nb]`` fp32 become
+    one int32 buffer in which owner ``o``'s block ``[Nq, n_o, Lq + 1]`` (the
+    winning tokens, then the bits of the score gradient) starts at word
+    ``col_start[o] * Nq * (Lq + 1)``; ``col_start [R + 1]`` int32 on the device
+    holds the first column of every owner."""
+    dev = _require_cuda(argmax, dscore, col_start)
+    a = argmax.contiguous()
+    g = dscore.contiguous().to(torch.float32)
+    cs = _i32(col_start)
+    Nq, Nb, Lq = a.shape
+    send = torch.empty((Nq * Nb * (Lq + 1),), dtype=torch.int32, device=dev)
+    with _on_device(dev):
+        rc = load_library().maxsim_b200_pack_owner_records(
+            _ptr(a), _ptr(g), _ptr(cs), cs.shape[0] - 1, Nq, Nb, Lq, _ptr(send), _stream_ptr())
+    _check(rc, "maxsim_b200_pack_owner_records")
+    return send
+
+
+def contrastive_backward_documents_from_records(records, queries, documents, document_offsets):
+    """grad_documents of this rank's ``documents`` from ``records [Nq_all, Nb_own,
+    Lq + 1]`` int32 (see :func:`pack_owner_records`) and the queries of all
+    ranks ``[Nq_all, Lq, D]``.  The gradient comes back in the inputs' 16-bit
+    type when the shape allows rounding once on store, else in fp32; None when
+    the kernel does not cover the shape."""
+    dev = _require_cuda(queries, records, documents, document_offsets)
+    q, d, off, Nq, Lq, Nb, dim = _contrastive_args(queries, documents, document_offsets)
+    r = records.contiguous()
+    if r.dtype != torch.int32 or r.numel() != Nq * Nb * (Lq + 1):
+        raise RuntimeError("records must be int32 [Nq, Nb, Lq + 1]")
+    lib = load_library()
+    for native in ((1, 0) if (_native_grads and q.dtype in (torch.float16, torch.bfloat16)) else (0,)):
+        dd = torch.empty(d.shape, dtype=q.dtype if native else torch.float32, device=dev)
+        with _on_device(dev):
+            rc = lib.maxsim_contrastive_backward_documents_from_records(
+                _ptr(r), _ptr(q), _ptr(d), _ptr(off), _ptr(dd), Nq, Lq, Nb, dim, d.shape[0],
+                _code(q), native, _stream_ptr())
+        if rc == 0:
+            return dd
+        if rc != _EUNSUPPORTED:
+            _check(rc, "maxsim_contrastive_backward_documents_from_records")
+    return None
 
 
 def contrastive_backward_part(dscore, queries, documents, document_offsets, argmax, *,

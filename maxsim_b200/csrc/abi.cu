@@ -11,6 +11,7 @@
 #include "common.cuh"
 #include "fwd_mma.cuh"
 #include "fwd_simt.cuh"
+#include "fwd_tc05_any.cuh"
 #include "fwd_tc05_doc.cuh"
 #include "group.cuh"
 #include "layout_stats.cuh"
@@ -76,6 +77,10 @@ int ensure_smem(Kernel kern, size_t smem, std::atomic<unsigned char>* done) {
   if (track) done[dev].store(1, std::memory_order_release);
   return MAXSIM_OK;
 }
+
+// Mean document length up to which contrastive argmax launches tile every
+// document on its own (measured on 1024 x 1024 pairs).
+constexpr int64_t kPerDocMaxMean = 256;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -154,30 +159,29 @@ int run_forward(const PairTable& t, float* scores, int32_t* argmax, int dtype, v
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int path = g_forward_path.load(std::memory_order_relaxed);
 
-  if (LAYOUT == kContrastive && path != 1 && path != 2 && tc05_eligible(t, dtype)) {
-    // Path 5 selects the M = 512 / 64-token-tile configuration (16 epilogue
-    // warps), kept for comparison; it measured slower than M = 256.
-    int variant = 0;
-    if (path == 5 && (t.n_pairs / t.C) >= 16) variant = 1;
-    if (path == 6) variant = 2;
-    if (path == 7) variant = 3;  // the earlier epilogue, for comparison
+  if (LAYOUT == kContrastive && path != 1 && path != 2 &&
+      (tc05_eligible(t, dtype) || tc05g_eligible(t, dtype))) {
     // Tiles that start at document starts pay one short tile per document and
-    // spare the epilogue its cuts at document boundaries: measured faster with
-    // argmax up to an average document length of about 256 tokens (1.43 against
-    // 1.83 ms for 1024 x 1024 pairs with 32-256 tokens per document), equal at
-    // 288, slower beyond, and slower for score-only launches at any length.
-    // Path 8 forces them, path 9 forces the boundary-agnostic tiles.
+    // spare the epilogue the cuts at document boundaries inside a tile; they are
+    // taken for argmax launches whose documents average at most kPerDocMaxMean
+    // tokens.  Path 8 forces them, path 9 forces the boundary-agnostic tiles.
     const bool per_document =
-        path == 8 || (path != 9 && variant == 0 && ARGMAX && t.d_rows <= 256 * (int64_t)t.C);
-    const int rc = per_document
-                       ? launch_tc05_doc<ARGMAX>(t, scores, argmax, dtype, sm_count(), st)
-                       : launch_tc05<ARGMAX>(t, scores, argmax, dtype, sm_count(), st, variant);
+        ARGMAX && (path == 8 || (path != 9 && t.block_rows <= kPerDocMaxMean * (int64_t)t.C));
+    int rc;
+    if (tc05_eligible(t, dtype))  // Lq = 32, dim = 128
+      rc = per_document ? launch_tc05_doc<ARGMAX>(t, scores, argmax, dtype, sm_count(), st)
+                        : launch_tc05<ARGMAX>(t, scores, argmax, dtype, sm_count(), st);
+    else
+      rc = launch_tc05g<ARGMAX>(t, scores, argmax, dtype, sm_count(), st, per_document);
     if (rc == 0) return launch_check("fwd_tc05_kernel");
     if (rc < 0) return fail(MAXSIM_ECUDA, "could not configure the tcgen05 kernel");
     // rc == 1: tensor maps could not be encoded; use the streaming kernel
   }
-  if ((path == 3 || (path >= 5 && path <= 9)) && LAYOUT == kContrastive)
+  if ((path == 3 || path == 8 || path == 9) && LAYOUT == kContrastive)
     return fail(MAXSIM_EUNSUPPORTED, "tcgen05 kernel forced but shape not eligible");
+  if (LAYOUT == kContrastive && (t.out_ld != t.C || t.out_col0 != 0))
+    return fail(MAXSIM_EUNSUPPORTED, "a column block of a wider score matrix needs the tcgen05 kernel "
+                                     "(float16 / bfloat16, Lq <= 64, dim %% 16 == 0, dim <= 128)");
 
   if (path != 1 && mma_eligible(t, dtype)) {
     if (dtype == MAXSIM_F16) return launch_mma<__half, LAYOUT, ARGMAX>(t, scores, argmax, st);
@@ -262,7 +266,7 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
         int gy, split;
         inv_grid_shape(Nb, d_rows / Nb, sm_count(), &gy, &split);
         dim3 grid((unsigned)Nb, (unsigned)gy);
-        kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 0, split);
+        kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 0, split, 0);
         return launch_check("bwd_dd_invert_kernel");
       }
       MAXSIM_CUDA(cudaMemsetAsync(dd, 0, (size_t)d_rows * dim * sizeof(float), st));
@@ -309,7 +313,8 @@ int run_backward_native_t(const PairTable& t, const float* dscore, const int32_t
   static_assert(LAYOUT == kPadded || LAYOUT == kContrastive, "padded and contrastive only");
   const int dim = t.dim;
   const bool ok = dim % 8 == 0 && dim <= 128 && aligned16(t.queries) && aligned16(t.documents) &&
-                  aligned16(dq) && aligned16(dd) && d_rows < (1ll << 31) && t.n_pairs > 0;
+                  aligned16(dq) && aligned16(dd) && d_rows < (1ll << 31) && t.n_pairs > 0 &&
+                  (dd || LAYOUT == kContrastive);
   if (!ok) return fail(MAXSIM_EUNSUPPORTED, "native-type gradients need dim %% 8 == 0, dim <= 128 and aligned tensors");
   const unsigned threads = kBwdWarps * 32;
   if constexpr (LAYOUT == kPadded) {
@@ -317,7 +322,7 @@ int run_backward_native_t(const PairTable& t, const float* dscore, const int32_t
       return fail(MAXSIM_EUNSUPPORTED, "native-type gradients need Lq_max <= 32 and Ld_max <= 1024");
   } else {
     const int64_t Nb = t.C;
-    if ((int64_t)Nq * t.q_slots > kInvEntries || Nq > kInvMaxQ || Nb >= (1ll << 31))
+    if (dd && ((int64_t)Nq * t.q_slots > kInvEntries || Nq > kInvMaxQ || Nb >= (1ll << 31)))
       return fail(MAXSIM_EUNSUPPORTED, "native-type gradients need Nq * Lq <= %d", kInvEntries);
   }
   {
@@ -331,6 +336,7 @@ int run_backward_native_t(const PairTable& t, const float* dscore, const int32_t
                                                                        reinterpret_cast<T*>(dd));
     return launch_check("bwd_dd_padded_native_kernel");
   } else {
+    if (!dd) return MAXSIM_OK;  // grad_queries only
     const int64_t Nb = t.C;
     auto kern = bwd_dd_invert_kernel<T>;
     constexpr size_t smem = inv_smem_bytes();
@@ -339,7 +345,7 @@ int run_backward_native_t(const PairTable& t, const float* dscore, const int32_t
     int gy, split;
     inv_grid_shape(Nb, d_rows / Nb, sm_count(), &gy, &split);
     dim3 grid((unsigned)Nb, (unsigned)gy);
-    kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 1, split);
+    kern<<<grid, kInvThreads, smem, st>>>(t, dscore, argmax, dd, (int)Nq, 1, split, 0);
     return launch_check("bwd_dd_invert_kernel");
   }
 }
@@ -350,13 +356,30 @@ int run_backward_native(const PairTable& t, const float* dscore, const int32_t* 
                         void* stream) {
   if (t.dim <= 0 || t.q_slots <= 0 || t.n_pairs < 0 || q_rows < 0 || d_rows < 0)
     return fail(MAXSIM_EINVAL, "sizes must be positive");
-  if (!dq || !dd || !dscore || !argmax) return fail(MAXSIM_EUNSUPPORTED, "empty problem");
+  // the contrastive operator may be asked for grad_queries alone (grad_documents NULL)
+  if (!dq || (!dd && LAYOUT != kContrastive) || !dscore || !argmax)
+    return fail(MAXSIM_EUNSUPPORTED, "empty problem");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   switch (dtype) {
     case MAXSIM_F16: return run_backward_native_t<__half, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
     case MAXSIM_BF16: return run_backward_native_t<__nv_bfloat16, LAYOUT>(t, dscore, argmax, dq, dd, q_rows, d_rows, Nq, st);
     default: return fail(MAXSIM_EUNSUPPORTED, "native-type gradients are for float16 / bfloat16 inputs");
   }
+}
+
+template <typename T>
+int launch_dd_from_records(const PairTable& t, const int32_t* records, void* dd, int64_t Nq,
+                           int native, cudaStream_t st) {
+  auto kern = bwd_dd_invert_kernel<T>;
+  constexpr size_t smem = inv_smem_bytes();
+  static std::atomic<unsigned char> configured[kMaxDevices];
+  if (int rc = ensure_smem(kern, smem, configured)) return rc;
+  int gy, split;
+  inv_grid_shape(t.C, t.d_rows / t.C, sm_count(), &gy, &split);
+  dim3 grid((unsigned)t.C, (unsigned)gy);
+  kern<<<grid, kInvThreads, smem, st>>>(t, nullptr, records, dd, (int)Nq, native, split,
+                                        t.q_slots + 1);
+  return launch_check("bwd_dd_invert_kernel");
 }
 
 PairTable packed_table(const void* q, const int32_t* qoff, const void* d, const int32_t* doff,
@@ -391,6 +414,7 @@ PairTable contrastive_table(const void* q, const void* d, const int32_t* doff, i
   t.n_pairs = Nq * Nb; t.dim = (int32_t)dim; t.q_slots = (int32_t)Lq;
   t.q_rows = Nq * Lq; t.d_rows = d_rows;
   t.Ld_max = 0; t.C = (int32_t)(Nb > 0 ? Nb : 1);
+  t.out_ld = t.C; t.out_col0 = 0; t.block_rows = d_rows;
   return t;
 }
 
@@ -806,6 +830,72 @@ int maxsim_contrastive_forward_with_argmax(const void* queries, const void* docu
   PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim,
                                   total_d_tokens);
   return run_forward<kContrastive, true>(t, scores, argmax, dtype, stream);
+}
+
+int maxsim_contrastive_forward_with_argmax_block(
+    const void* queries, const void* documents, const int32_t* document_offsets, float* scores,
+    int32_t* argmax, int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim, int64_t total_d_tokens,
+    int64_t block_tokens, int64_t out_ld, int64_t out_col0, int dtype, void* stream) {
+  if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
+      !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
+  if (out_col0 < 0 || out_ld < out_col0 + Nb || !fits_i32(out_ld))
+    return fail(MAXSIM_EINVAL, "the block's columns [%lld, %lld) do not fit a row of %lld",
+                (long long)out_col0, (long long)(out_col0 + Nb), (long long)out_ld);
+  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim,
+                                  total_d_tokens);
+  t.out_ld = out_ld;
+  t.out_col0 = out_col0;
+  t.block_rows = block_tokens > 0 ? block_tokens : total_d_tokens;
+  return run_forward<kContrastive, true>(t, scores, argmax, dtype, stream);
+}
+
+int maxsim_b200_pack_owner_records(const int32_t* argmax, const float* dscore,
+                                   const int32_t* col_start, int64_t n_owners, int64_t Nq,
+                                   int64_t Nb, int64_t Lq, int32_t* send, void* stream) {
+  if (n_owners <= 0 || Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(Nq) || !fits_i32(Nb) ||
+      !fits_i32(Lq) || !fits_i32(n_owners))
+    return fail(MAXSIM_EINVAL, "sizes must be >= 0 (Lq, n_owners > 0) and fit int32");
+  if (Nq * Nb == 0) return MAXSIM_OK;
+  if (!argmax || !dscore || !col_start || !send) return fail(MAXSIM_EINVAL, "null pointer argument");
+  const int64_t pairs = Nq * Nb;
+  const int64_t grid = (pairs + 7) / 8;
+  if (grid >= (1ll << 31)) return fail(MAXSIM_EINVAL, "too many pairs");
+  pack_owner_records_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      argmax, dscore, col_start, (int)n_owners, (int)Nq, (int)Nb, (int)Lq, send);
+  return launch_check("pack_owner_records_kernel");
+}
+
+int maxsim_contrastive_backward_documents_from_records(
+    const int32_t* records, const void* queries, const void* documents,
+    const int32_t* document_offsets, void* grad_documents, int64_t Nq, int64_t Lq, int64_t Nb,
+    int64_t dim, int64_t total_d_tokens, int dtype, int native, void* stream) {
+  if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
+      !fits_i32(total_d_tokens) || !fits_i32(Nq))
+    return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
+  if (!valid_dtype(dtype)) return fail(MAXSIM_EINVAL, "unknown dtype code %d", dtype);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t elem = native ? (dtype == MAXSIM_F32 ? 4 : 2) : 4;
+  if (Nq * Nb == 0) {
+    if (grad_documents && total_d_tokens)
+      MAXSIM_CUDA(cudaMemsetAsync(grad_documents, 0, (size_t)total_d_tokens * dim * elem, st));
+    return MAXSIM_OK;
+  }
+  if (!records || !queries || !documents || !document_offsets || !grad_documents)
+    return fail(MAXSIM_EINVAL, "null pointer argument");
+  PairTable t = contrastive_table(queries, documents, document_offsets, Nq, Lq, Nb, dim,
+                                  total_d_tokens);
+  const bool ok = dim % 8 == 0 && aligned16(queries) && aligned16(grad_documents) &&
+                  Lq <= kInvEntries && Nq * Lq < (1ll << 31) && (Nq + 1) * Nb * (Lq + 1) < (1ll << 62);
+  if (!ok) return fail(MAXSIM_EUNSUPPORTED, "record routing needs dim %% 8 == 0 and aligned tensors");
+  if (native && (dtype == MAXSIM_F32 || Nq * Lq > kInvEntries || Nq > kInvMaxQ || dim > 128))
+    return fail(MAXSIM_EUNSUPPORTED, "native-type gradients need float16 / bfloat16, Nq * Lq <= %d and dim <= 128",
+                kInvEntries);
+  switch (dtype) {
+    case MAXSIM_F32: return launch_dd_from_records<float>(t, records, grad_documents, Nq, 0, st);
+    case MAXSIM_F16: return launch_dd_from_records<__half>(t, records, grad_documents, Nq, native, st);
+    default: return launch_dd_from_records<__nv_bfloat16>(t, records, grad_documents, Nq, native, st);
+  }
 }
 
 int maxsim_contrastive_backward(const float* dscore, const void* queries, const void* documents,

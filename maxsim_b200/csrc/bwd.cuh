@@ -686,7 +686,11 @@ template <typename T>
 __global__ void __launch_bounds__(kInvThreads, 2)
 bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
                      const int32_t* __restrict__ argmax, void* __restrict__ dd_out, int Nq,
-                     int native, int split) {
+                     int native, int split, int rec_stride) {
+  // rec_stride > 0: `argmax` holds one record of rec_stride words per pair -- the Lq
+  // winning tokens followed by the bits of the pair's score gradient -- and `dscore`
+  // is not read (the form in which a rank receives the pairs of its own documents
+  // from the ranks that hold the queries).
   // CTA (d, y) takes the token chunks y, y + gridDim.y, ... of document d.  A chunk
   // is kInvBins tokens, or, with `split` set (few documents, several CTAs per
   // document), an even share of the document.
@@ -717,10 +721,13 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
     for (int q0 = 0; q0 < Nq; q0 += q_block) {
       const int nq = min(q_block, Nq - q0);
       const int n_e = nq * Lq;
-      const int32_t* amax = argmax + ((int64_t)q0 * Nb + d) * Lq;  // entry (q, i) at amax[q*Nb*Lq + i]
+      const int rs = rec_stride > 0 ? rec_stride : Lq;                // words per pair in `argmax`
+      const int32_t* amax = argmax + ((int64_t)q0 * Nb + d) * rs;     // entry (q, i) at amax[q*Nb*rs + i]
       __syncthreads();
       for (int b = tid; b < ntok; b += kInvThreads) cursor[b] = 0;
-      for (int qq = tid; qq < nq; qq += kInvThreads) gcol[qq] = __ldg(dscore + (int64_t)(q0 + qq) * Nb + d);
+      for (int qq = tid; qq < nq; qq += kInvThreads)
+        gcol[qq] = rec_stride > 0 ? __int_as_float(__ldg(amax + (int64_t)qq * Nb * rs + Lq))
+                                  : __ldg(dscore + (int64_t)(q0 + qq) * Nb + d);
       if (tid == 0) *next_tok = 0;
       __syncthreads();
       // histogram of winning tokens
@@ -732,7 +739,7 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
           a[u] = -1;
           if (e < n_e) {
             const int qq = e / Lq, i = e - qq * Lq;
-            a[u] = __ldg(amax + (int64_t)qq * Nb * Lq + i) - tok0;
+            a[u] = __ldg(amax + (int64_t)qq * Nb * rs + i) - tok0;
           }
         }
 #pragma unroll
@@ -771,7 +778,7 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
           a[u] = -1;
           if (e < n_e) {
             const int qq = e / Lq, i = e - qq * Lq;
-            a[u] = __ldg(amax + (int64_t)qq * Nb * Lq + i) - tok0;
+            a[u] = __ldg(amax + (int64_t)qq * Nb * rs + i) - tok0;
           }
         }
 #pragma unroll
@@ -848,6 +855,35 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
       }
     }
   }
+}
+
+// ---------------------------------------------------------------------------
+// Sharded contrastive training, owner exchange: the pairs of this rank's
+// queries are regrouped by the rank that owns the document.  Owner o's block
+// starts at word col_start[o] * Nq * (Lq + 1) of `send` and is laid out
+// [query][document of o][Lq + 1]: the Lq winning tokens of the pair and the
+// bits of its score gradient.  Blocks of all ranks' queries, concatenated in
+// rank order by the all-to-all, are the [all queries][own documents][Lq + 1]
+// tensor that bwd_dd_invert_kernel reads with rec_stride = Lq + 1.
+// One warp per pair.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+pack_owner_records_kernel(const int32_t* __restrict__ argmax, const float* __restrict__ dscore,
+                          const int32_t* __restrict__ col_start, int n_owners, int Nq, int Nb, int Lq,
+                          int32_t* __restrict__ send) {
+  const int lane = threadIdx.x & 31;
+  const int64_t pair = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (pair >= (int64_t)Nq * Nb) return;
+  const int q = (int)(pair / Nb), c = (int)(pair - (int64_t)q * Nb);
+  // owner of column c: the last o with col_start[o] <= c (few owners: a scan)
+  int o = 0;
+  while (o + 1 < n_owners && __ldg(col_start + o + 1) <= c) ++o;
+  const int c0 = __ldg(col_start + o), n_o = __ldg(col_start + o + 1) - c0;
+  const int rec = Lq + 1;
+  int32_t* dst = send + ((int64_t)c0 * Nq + (int64_t)q * n_o + (c - c0)) * rec;
+  const int32_t* src = argmax + pair * Lq;
+  for (int i = lane; i < Lq; i += 32) dst[i] = __ldg(src + i);
+  if (lane == 0) dst[Lq] = __float_as_int(__ldg(dscore + pair));
 }
 
 }  // namespace maxsim

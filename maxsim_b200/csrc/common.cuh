@@ -46,6 +46,13 @@ struct PairTable {
   int32_t q_slots;   // argmax slots per pair: Lq_max / max_q_len / Lq
   int32_t Ld_max;    // padded only
   int32_t C;         // padded: candidates per query; contrastive: Nb
+  // contrastive forward only: pair (q, d) is written to output slot
+  // q * out_ld + out_col0 + d, so that launches over different document ranges
+  // fill column blocks of one [Nq, out_ld] score matrix (out_ld = Nb, out_col0 =
+  // 0 for the ordinary operator).  Only the tcgen05 kernel honours other values.
+  int64_t out_ld;
+  int64_t out_col0;
+  int64_t block_rows;  // document rows this launch covers (d_rows unless a block of a larger tensor)
 };
 
 struct PairGeom {

@@ -334,7 +334,7 @@ fwd_mma_kernel(PairTable t, float* __restrict__ scores, int32_t* __restrict__ ar
       }
       const int rows = a_rows;
 
-      if (!mbar_wait(bars_u32 + 8 * s, parity)) break;
+      if (!__all_sync(0xffffffffu, mbar_wait(bars_u32 + 8 * s, parity))) break;  // leave together
 
       float acc[2][2][4];
 #pragma unroll

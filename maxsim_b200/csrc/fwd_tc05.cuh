@@ -1,4 +1,7 @@
-// Contrastive forward on the 5th-generation tensor cores (tcgen05 + TMEM).
+// Contrastive forward on the 5th-generation tensor cores (tcgen05 + TMEM),
+// specialised for the late-interaction shape Lq = 32, dim = 128 (other query
+// lengths and dims take the general kernel in fwd_tc05_any.cuh, which measures
+// 5-10 % slower on this shape).
 //
 // All-pairs scoring of rectangular queries [Nq, 32, 128] against packed
 // documents [T_d, 128] is a dense contraction with only 256 flop per
@@ -53,14 +56,12 @@ constexpr int kAccStages = 2;
 constexpr int kABoxBytes = kBM * 128;  // one 128-row x 64-element box of the query block: 16 KB
 constexpr uint32_t kWaitLimit = 1u << 22;
 
-// A kernel configuration: MSUB accumulators of 128 rows per CTA (M = 128*MSUB)
-// and document tiles of BN tokens.  TMEM holds MSUB*BN*2 columns (<= 512).
-//   <2, 128>: M = 256,  8 epilogue warps, each folds 128 columns per tile (default)
-//   <4,  64>: M = 512, 16 epilogue warps, each folds  64 columns per tile; kept
-//             for comparison -- its shorter MMAs and single register buffer
-//             measured slower (TMA/MMA pipeline alone: 0.61 of peak).
+// The kernel's configuration: MSUB = 2 accumulators of 128 rows per CTA (M = 256)
+// and document tiles of BN = 128 tokens; TMEM holds MSUB * BN * 2 = 512 columns;
+// eight epilogue warps, each folding 128 columns per tile.
 template <int MSUB, int BN>
 struct Cfg {
+  static_assert(MSUB == 2 && BN == 128, "one configuration");
   static constexpr int kMSub = MSUB;
   static constexpr int kBN = BN;
   static constexpr int kQPerCta = kQPerSub * MSUB;
@@ -72,17 +73,12 @@ struct Cfg {
   static constexpr int kBBoxBytes = BN * 128;          // one BN-row x 64-element box
   static constexpr int kBTileBytes = 2 * kBBoxBytes;
   static constexpr int kATileBytes = 2 * kABoxBytes;   // 32 KB per accumulator
-  // <2, 64> is the two-CTAs-per-SM configuration: half the shared memory and
-  // half the TMEM columns per CTA, so two CTAs (16 epilogue warps) share an SM.
-  static constexpr bool kTwoPerSm = (MSUB == 2 && BN == 64);
-  static constexpr int kBStages = kTwoPerSm ? 2 : 4;
-  static constexpr int kMinBlocks = kTwoPerSm ? 2 : 1;
+  static constexpr int kBStages = 4;
+  static constexpr int kMinBlocks = 1;
   static constexpr size_t kSmemA = (size_t)MSUB * kATileBytes;
   static constexpr size_t kSmemB = (size_t)kBStages * kBTileBytes;
   static constexpr size_t kSmemBytes = kSmemA + kSmemB + 1024 /*alignment slack*/ + 256 /*barriers*/;
-  static constexpr bool kPrefetch = (MSUB <= 2) && !kTwoPerSm;  // second TMEM register buffer only if registers allow
   static_assert(kTmemCols <= 512 && (kTmemCols & (kTmemCols - 1)) == 0, "TMEM columns");
-  static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "tile tokens");
 };
 
 __device__ __forceinline__ bool wait_bounded(uint32_t bar, uint32_t parity) {
@@ -134,33 +130,6 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-// tcgen05.ld is asynchronous: its destination registers may only be read after
-// tcgen05.wait::ld.  The wait takes the registers as in/out operands so that
-// the compiler cannot schedule a use of them ahead of it.
-__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_ld_wait(uint32_t (&r)[32]) {
-  asm volatile("tcgen05.wait::ld.sync.aligned;"
-               : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]),
-                 "+r"(r[6]), "+r"(r[7]), "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]),
-                 "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]), "+r"(r[16]), "+r"(r[17]),
-                 "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-                 "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]),
-                 "+r"(r[30]), "+r"(r[31])
-               :
-               : "memory");
-}
-
 __device__ __forceinline__ float max3(float a, float b, float c) {
   float d;
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));  // NaN operands are ignored
@@ -195,6 +164,9 @@ __device__ __forceinline__ int first_index_of_max(const float (&v)[32], float m)
 }
 
 // 64-column TMEM load (two of them bring a whole 128-token tile to registers).
+// tcgen05.ld is asynchronous: its destination registers may only be read after
+// tcgen05.wait::ld.  The wait takes the registers as in/out operands so that
+// the compiler cannot schedule a use of them ahead of it.
 __device__ __forceinline__ void tmem_ld64_issue(uint32_t taddr, uint32_t (&r)[64]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x64.b32 "
@@ -232,105 +204,11 @@ __device__ __forceinline__ void tmem_ld_wait64(uint32_t (&r)[64]) {
                : "memory");
 }
 
-// Fold 64 similarities (two chunks of 32, a before b) of one document.
-template <bool ARGMAX>
-__device__ __forceinline__ void fold64(const float (&a)[32], const float (&b)[32], int base_ix,
-                                       float& run, int& idx) {
-  const float m = fmaxf(max32(a), max32(b));
-  if (ARGMAX) {
-    if (__any_sync(0xffffffffu, m > run)) {
-      const float kScale = 8.507059173023462e37f;  // 2^126
-      float ka[32], kb[32];
-#pragma unroll
-      for (int j = 0; j < 32; ++j) {
-        ka[j] = fmaf(a[j] - m, kScale, 8388608.0f + (float)(63 - j));
-        kb[j] = fmaf(b[j] - m, kScale, 8388608.0f + (float)(31 - j));
-      }
-      const float k = fmaxf(max32(ka), max32(kb));
-      if (m > run) {
-        int first;
-        if (k >= 8388608.0f) {
-          first = 63 - (__float_as_int(k) & 63);
-        } else {  // infinite maximum: compare loop
-          first = 63;
-#pragma unroll
-          for (int j = 31; j >= 0; --j) first = (b[j] == m) ? 32 + j : first;
-#pragma unroll
-          for (int j = 31; j >= 0; --j) first = (a[j] == m) ? j : first;
-        }
-        run = m;
-        idx = base_ix + first;
-      }
-    }
-  } else {
-    run = fmaxf(run, m);
-  }
-}
-
-// Fold a whole 128-column tile of one document (four chunks a, b, c, d in order).
-template <bool ARGMAX>
-__device__ __forceinline__ void fold128(const float (&a)[32], const float (&b)[32],
-                                        const float (&c)[32], const float (&d)[32], int base_ix,
-                                        float& run, int& idx) {
-  const float m = fmaxf(fmaxf(max32(a), max32(b)), fmaxf(max32(c), max32(d)));
-  if (ARGMAX) {
-    if (__any_sync(0xffffffffu, m > run)) {
-      const float kScale = 8.507059173023462e37f;  // 2^126
-      float k4[4];
-      {
-        float t[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) t[j] = fmaf(a[j] - m, kScale, 8388608.0f + (float)(127 - j));
-        k4[0] = max32(t);
-      }
-      {
-        float t[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) t[j] = fmaf(b[j] - m, kScale, 8388608.0f + (float)(95 - j));
-        k4[1] = max32(t);
-      }
-      {
-        float t[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) t[j] = fmaf(c[j] - m, kScale, 8388608.0f + (float)(63 - j));
-        k4[2] = max32(t);
-      }
-      {
-        float t[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) t[j] = fmaf(d[j] - m, kScale, 8388608.0f + (float)(31 - j));
-        k4[3] = max32(t);
-      }
-      const float k = fmaxf(fmaxf(k4[0], k4[1]), fmaxf(k4[2], k4[3]));
-      if (m > run) {
-        int first;
-        if (k >= 8388608.0f) {
-          first = 127 - (__float_as_int(k) & 127);
-        } else {  // infinite maximum: compare loop
-          first = 127;
-#pragma unroll
-          for (int j = 31; j >= 0; --j) first = (d[j] == m) ? 96 + j : first;
-#pragma unroll
-          for (int j = 31; j >= 0; --j) first = (c[j] == m) ? 64 + j : first;
-#pragma unroll
-          for (int j = 31; j >= 0; --j) first = (b[j] == m) ? 32 + j : first;
-#pragma unroll
-          for (int j = 31; j >= 0; --j) first = (a[j] == m) ? j : first;
-        }
-        run = m;
-        idx = base_ix + first;
-      }
-    }
-  } else {
-    run = fmaxf(run, m);
-  }
-}
-
-// The same folds with a cheaper index search.  Once the maximum m of the tile
-// is known, the first 32-column chunk whose own maximum equals m holds the
-// first index; its 32 values are picked per lane with select instructions
+// Folds of 64 and 128 similarities of one document.  Once the maximum m of the
+// columns is known, the first 32-column chunk whose own maximum equals m holds
+// the first index; its 32 values are picked per lane with select instructions
 // (one per column for 64 columns, three for 128) and only they go through the
-// FMA-pipe key search: about 1.9 instructions per similarity instead of 3.
+// FMA-pipe key search: about 1.9 instructions per similarity.
 template <bool ARGMAX>
 __device__ __forceinline__ void fold64_sel(const float (&a)[32], const float (&b)[32], int base_ix,
                                            float& run, int& idx) {
@@ -423,13 +301,15 @@ struct Params {
   int32_t n_qgroups;      // ceil(Nq / queries per CTA)
   int32_t docs_per_item;
   int32_t n_items;        // document runs x query groups, query group fastest
+  int32_t out_ld;         // the pair (q, d) is output slot q * out_ld + out_col0 + d
+  int32_t out_col0;
   uint32_t idesc;
 };
 
-// MODE bit 0: select-then-search argmax folds; bit 1: the producer warpgroup
-// gives most of its registers to the epilogue warps (setmaxnreg), which then
-// hold a whole tile plus the fold's temporaries without spilling.
-template <bool ARGMAX, int MSUB, int BN, int MODE = 0>
+// The producer warpgroup gives most of its registers to the epilogue warps
+// (setmaxnreg), which then hold a whole tile plus the fold's temporaries
+// without spilling.
+template <bool ARGMAX, int MSUB, int BN>
 __global__ void __launch_bounds__(Cfg<MSUB, BN>::kThreads, Cfg<MSUB, BN>::kMinBlocks)
 fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_d,
                 const Params P) {
@@ -438,9 +318,12 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   constexpr int kTmemCols = C::kTmemCols, kQPerCta = C::kQPerCta;
   constexpr size_t kSmemA = C::kSmemA, kSmemB = C::kSmemB;
   (void)kQPerCta;
-  constexpr bool SELECT = (MODE & 1) != 0;
-  constexpr bool REALLOC = (MODE & 2) != 0;
-  static_assert(!REALLOC || (C::kThreads == 384 && C::kMinBlocks == 1), "register hand-over is sized for 12 warps");
+  // Register hand-over: the CTA owns 384 x 168 registers from launch; the producer warpgroup
+  // drops to 40 per thread, which frees exactly the 2 x 128 x 64 registers the two epilogue
+  // warpgroups need to grow to 232.  setmaxnreg.inc waits, without limit, until that many
+  // registers are free: the three numbers have to balance.
+  static_assert(C::kThreads == 384 && 128 * (168 - 40) == 256 * (232 - 168),
+                "register hand-over does not balance");
   extern __shared__ unsigned char tc05_smem_raw[];
   const uint32_t raw = smem_u32(tc05_smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
@@ -488,7 +371,7 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // query-block reloads measured slower.)
 
   if (warp < C::kProducerWarps) {
-  if constexpr (REALLOC) asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
   if (warp == 0) {
     // ===================== TMA producer ====================================
     if (lane == 0) {
@@ -557,17 +440,17 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   } else {
     // ===================== epilogue ========================================
-    if constexpr (REALLOC) asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
     const int ew = warp - C::kProducerWarps;
     const int sub = ew >> 2;
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     uint32_t acc = 0, aph = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < P.n_items; item += gridDim.x) {
+    for (int item = blockIdx.x; item < P.n_items; item += gridDim.x) {
       const int dc = item / P.n_qgroups, qg = item - dc * P.n_qgroups;
       const int d_lo = dc * P.docs_per_item, d_hi = min(P.Nb, d_lo + P.docs_per_item);
       const int s0 = __ldg(doff + d_lo), s1 = __ldg(doff + d_hi);
-      const int ntiles = (s1 - s0 + kBN - 1) / kBN;
+      const int ntiles = ok ? (s1 - s0 + kBN - 1) / kBN : 0;
       const int q = (qg * kMSub + sub) * kQPerSub + quad;  // this warp's query
       const bool q_ok = q < P.Nq;
 
@@ -578,7 +461,7 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       int idx = 0;
 
       for (int tile = 0; tile < ntiles; ++tile) {
-        if (!wait_bounded(t_full + 8 * acc, aph)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, wait_bounded(t_full + 8 * acc, aph))) { ok = false; break; }  // leave together
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t taddr0 =
             tmem_base + ((uint32_t)(quad * 32) << 16) + acc * (kMSub * kBN) + sub * kBN;
@@ -592,7 +475,7 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 #pragma unroll
           for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
           if (q_ok) {
-            const int64_t pair = (int64_t)q * P.Nb + d;
+            const int64_t pair = (int64_t)q * P.out_ld + P.out_col0 + d;
             if (ARGMAX) P.argmax[pair * kLq + lane] = idx;
             if (lane == 0) P.scores[pair] = sum;
           }
@@ -635,81 +518,59 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         };
 
-        if constexpr (kBN == 128 && C::kPrefetch) {
-          // The whole tile goes to registers at once and the TMEM stage is handed
-          // back before any arithmetic, so the tensor pipe never waits on the fold.
-          uint32_t raw[2][64];
-          if (n_valid > 0) {
-            tmem_ld64_issue(taddr0, raw[0]);
-            if (n_valid > 64) tmem_ld64_issue(taddr0 + 64, raw[1]);
-            tmem_ld_wait64(raw[0]);
-            tmem_ld_wait64(raw[1]);
-          }
-          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-          __syncwarp();
-          if (lane == 0) mbar_arrive(t_empty + 8 * acc);
-          if (n_valid > 0) {
-            float va[32], vb[32], vc[32], vd[32];
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              va[j] = __uint_as_float(raw[0][j]);
-              vb[j] = __uint_as_float(raw[0][32 + j]);
-              vc[j] = __uint_as_float(raw[1][j]);
-              vd[j] = __uint_as_float(raw[1][32 + j]);
-            }
-            if (d < d_hi && tok_tile + 128 <= dend) {
-              if constexpr (SELECT) fold128_sel<ARGMAX>(va, vb, vc, vd, tok_tile - dstart, run, idx);
-              else fold128<ARGMAX>(va, vb, vc, vd, tok_tile - dstart, run, idx);
-              if (tok_tile + 128 == dend) finish_document();
-            } else {
-              if (d < d_hi && tok_tile + 64 <= dend) {
-                if constexpr (SELECT) fold64_sel<ARGMAX>(va, vb, tok_tile - dstart, run, idx);
-                else fold64<ARGMAX>(va, vb, tok_tile - dstart, run, idx);
-                if (tok_tile + 64 == dend) finish_document();
-              } else {
-                fold_chunk(va, tok_tile);
-                if (32 < n_valid) fold_chunk(vb, tok_tile + 32);
-              }
-              if (64 < n_valid) {
-                if (d < d_hi && tok_tile + 128 <= dend) {
-                  if constexpr (SELECT) fold64_sel<ARGMAX>(vc, vd, tok_tile + 64 - dstart, run, idx);
-                  else fold64<ARGMAX>(vc, vd, tok_tile + 64 - dstart, run, idx);
-                  if (tok_tile + 128 == dend) finish_document();
-                } else {
-                  fold_chunk(vc, tok_tile + 64);
-                  if (96 < n_valid) fold_chunk(vd, tok_tile + 96);
-                }
-              }
-            }
-          }
-          if (++acc == kAccStages) { acc = 0; aph ^= 1u; }
-          continue;
-        } else {
-          // 32 columns per step
-          constexpr int kBufs = C::kPrefetch ? 2 : 1;
-          uint32_t raw[kBufs][32];
-          const int n_chunks = (n_valid + 31) >> 5;
-          if (C::kPrefetch && n_chunks > 0) tmem_ld32_issue(taddr0, raw[0]);
-#pragma unroll
-          for (int c4 = 0; c4 < kBN / 32; ++c4) {
-            if (c4 < n_chunks) {
-              constexpr int kNoBuf = 0;
-              const int cur = C::kPrefetch ? (c4 & 1) : kNoBuf;
-              if (!C::kPrefetch) tmem_ld32_issue(taddr0 + c4 * 32, raw[0]);
-              tmem_ld_wait(raw[cur]);
-              if (C::kPrefetch && c4 + 1 < n_chunks)
-                tmem_ld32_issue(taddr0 + (c4 + 1) * 32, raw[(c4 + 1) & (kBufs - 1)]);
-              float v[32];
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[cur][j]);
-              fold_chunk(v, tok_tile + c4 * 32);
-            }
-          }
+        // The whole tile goes to registers at once and the TMEM stage is handed
+        // back before any arithmetic, so the tensor pipe never waits on the fold.
+        uint32_t raw[2][64];
+        if (n_valid > 0) {
+          tmem_ld64_issue(taddr0, raw[0]);
+          if (n_valid > 64) tmem_ld64_issue(taddr0 + 64, raw[1]);
+          tmem_ld_wait64(raw[0]);
+          tmem_ld_wait64(raw[1]);
         }
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
         __syncwarp();
         if (lane == 0) mbar_arrive(t_empty + 8 * acc);
         if (++acc == kAccStages) { acc = 0; aph ^= 1u; }
+        if (n_valid > 0) {
+          float va[32], vb[32], vc[32], vd[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            va[j] = __uint_as_float(raw[0][j]);
+            vb[j] = __uint_as_float(raw[0][32 + j]);
+            vc[j] = __uint_as_float(raw[1][j]);
+            vd[j] = __uint_as_float(raw[1][32 + j]);
+          }
+          if (d < d_hi && tok_tile + 128 <= dend) {
+            fold128_sel<ARGMAX>(va, vb, vc, vd, tok_tile - dstart, run, idx);
+            if (tok_tile + 128 == dend) finish_document();
+          } else {
+            if (d < d_hi && tok_tile + 64 <= dend) {
+              fold64_sel<ARGMAX>(va, vb, tok_tile - dstart, run, idx);
+              if (tok_tile + 64 == dend) finish_document();
+            } else {
+              fold_chunk(va, tok_tile);
+              if (32 < n_valid) fold_chunk(vb, tok_tile + 32);
+            }
+            if (64 < n_valid) {
+              if (d < d_hi && tok_tile + 128 <= dend) {
+                fold64_sel<ARGMAX>(vc, vd, tok_tile + 64 - dstart, run, idx);
+                if (tok_tile + 128 == dend) finish_document();
+              } else {
+                fold_chunk(vc, tok_tile + 64);
+                if (96 < n_valid) fold_chunk(vd, tok_tile + 96);
+              }
+            }
+          }
+        }
+      }
+      // Documents of the item that no tile finished: documents without tokens at its end, or,
+      // after a wait that ran out, everything this warp did not get to (NaN scores then).
+      if (q_ok) {
+        for (; d < d_hi; ++d) {
+          const int64_t pair = (int64_t)q * P.out_ld + P.out_col0 + d;
+          if (ARGMAX) P.argmax[pair * kLq + lane] = 0;
+          if (lane == 0) P.scores[pair] = ok ? neg_inf() : __int_as_float(0x7fc00000);
+        }
       }
     }
   }
@@ -770,6 +631,7 @@ inline bool tc05_eligible(const PairTable& t, int dtype) {
   const int64_t Nb = t.C, Nq = t.n_pairs / (Nb > 0 ? Nb : 1);
   if (Nq < 8 || Nb < 1) return false;
   if (t.d_rows <= 0 || t.d_rows >= (1ll << 31) || Nq * tc05::kLq >= (1ll << 31)) return false;
+  if (t.out_ld * Nq >= (1ll << 31)) return false;
   return tensor_map_encoder() != nullptr;
 }
 
@@ -793,6 +655,8 @@ inline bool tc05_fill_params(const PairTable& t, float* scores, int32_t* argmax,
   const int64_t n_items = n_dc * P->n_qgroups;
   if (n_items >= (1ll << 31)) return false;
   P->n_items = (int32_t)n_items;
+  P->out_ld = (int32_t)t.out_ld;
+  P->out_col0 = (int32_t)t.out_col0;
   const uint32_t fmt = dtype == 2 ? 1u : 0u;  // bf16 : fp16
   P->idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(bn >> 3) << 17) |
              ((uint32_t)(tc05::kBM >> 4) << 24);
@@ -817,45 +681,24 @@ int tc05_configure(Kernel kern, size_t smem, std::atomic<unsigned char> (&config
 
 // Returns 0 on success, 1 if the launch could not be prepared (caller falls
 // back to another kernel), or a CUDA error code < 0.
-template <bool ARGMAX, int MSUB, int BN, int MODE = 0>
-int launch_tc05_cfg(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
-                    cudaStream_t st) {
-  using C = tc05::Cfg<MSUB, BN>;
+template <bool ARGMAX>
+int launch_tc05(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
+                cudaStream_t st) {
+  using C = tc05::Cfg<2, 128>;
   const int64_t Nq = t.n_pairs / t.C;
   CUtensorMap tm_q, tm_d;
   const bool bf16 = dtype == 2;
   if (!encode_rows128(&tm_q, t.queries, Nq * tc05::kLq, tc05::kBM, bf16)) return 1;
-  if (!encode_rows128(&tm_d, t.documents, t.d_rows, BN, bf16)) return 1;
+  if (!encode_rows128(&tm_d, t.documents, t.d_rows, C::kBN, bf16)) return 1;
   tc05::Params P;
-  if (!tc05_fill_params(t, scores, argmax, dtype, sms, C::kQPerCta, BN, &P)) return 1;
+  if (!tc05_fill_params(t, scores, argmax, dtype, sms, C::kQPerCta, C::kBN, &P)) return 1;
 
-  auto kern = tc05::fwd_tc05_kernel<ARGMAX, MSUB, BN, MODE>;
+  auto kern = tc05::fwd_tc05_kernel<ARGMAX, 2, 128>;
   static std::atomic<unsigned char> configured[64];
   if (int rc = tc05_configure(kern, C::kSmemBytes, configured)) return rc;
-  const int64_t slots = (int64_t)sms * C::kMinBlocks;
-  const int grid = (int)(P.n_items < slots ? P.n_items : slots);
+  const int grid = (int)(P.n_items < sms ? P.n_items : sms);
   kern<<<grid, C::kThreads, C::kSmemBytes, st>>>(tm_q, tm_d, P);
   return 0;
-}
-
-// variant 0: M = 256, 128-token tiles, one CTA per SM, the producer warpgroup's
-//            registers handed to the epilogue warps, select-then-search argmax
-//            folds (default)
-// variant 1: M = 512, 64-token tiles, 16 epilogue warps
-// variant 2: M = 256, 64-token tiles, two CTAs per SM
-// variant 3: variant 0 without the register hand-over and with the full-width
-//            argmax search (the earlier epilogue, kept for comparison)
-template <bool ARGMAX>
-int launch_tc05(const PairTable& t, float* scores, int32_t* argmax, int dtype, int sms,
-                cudaStream_t st, int variant) {
-  if (variant == 1) return launch_tc05_cfg<ARGMAX, 4, 64>(t, scores, argmax, dtype, sms, st);
-  if (variant == 2) return launch_tc05_cfg<ARGMAX, 2, 64>(t, scores, argmax, dtype, sms, st);
-  if constexpr (ARGMAX) {
-    if (variant == 3) return launch_tc05_cfg<true, 2, 128, 0>(t, scores, argmax, dtype, sms, st);
-    return launch_tc05_cfg<true, 2, 128, 3>(t, scores, argmax, dtype, sms, st);
-  } else {
-    return launch_tc05_cfg<false, 2, 128, 2>(t, scores, argmax, dtype, sms, st);
-  }
 }
 
 }  // namespace maxsim

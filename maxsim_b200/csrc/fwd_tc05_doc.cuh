@@ -17,7 +17,7 @@
 // rows (rows past the document's end belong to the next document or are
 // zero-filled past the end of the tensor; their columns are never read from
 // TMEM).  Roles, barriers, register hand-over and bounded waits are those of
-// fwd_tc05_kernel<.., 2, 128, 3>.
+// fwd_tc05_kernel.
 #pragma once
 
 #include "fwd_tc05.cuh"
@@ -213,21 +213,22 @@ fwd_tc05_doc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
     const int quad = warp & 3;  // TMEM lane quadrant this warp may read
     uint32_t acc = 0, aph = 0;
     bool ok = true;
-    for (int item = blockIdx.x; ok && item < P.n_items; item += gridDim.x) {
+    for (int item = blockIdx.x; item < P.n_items; item += gridDim.x) {  // goes on after a wait
+      // ran out: the pairs this warp does not get to are given NaN scores
       const int dc = item / P.n_qgroups, qg = item - dc * P.n_qgroups;
       const int d_lo = dc * P.docs_per_item, d_hi = min(P.Nb, d_lo + P.docs_per_item);
       const int q = (qg * kMSub + sub) * kQPerSub + quad;  // this warp's query
       const bool q_ok = q < P.Nq;
       int dbeg = __ldg(doff + d_lo);
       int dend_next = __ldg(doff + d_lo + 1);
-      for (int d = d_lo; ok && d < d_hi; ++d) {
+      for (int d = d_lo; d < d_hi; ++d) {
         const int dend = dend_next;
         if (d + 1 < d_hi) dend_next = __ldg(doff + d + 2);
         const int Ld = dend - dbeg;
         float run = neg_inf();
         int idx = 0;
-        for (int t0 = 0; t0 < Ld; t0 += kBN) {
-          if (!wait_bounded(t_full + 8 * acc, aph)) { ok = false; break; }
+        for (int t0 = 0; ok && t0 < Ld; t0 += kBN) {
+          if (!__all_sync(0xffffffffu, wait_bounded(t_full + 8 * acc, aph))) { ok = false; break; }  // leave together
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t taddr0 =
               tmem_base + ((uint32_t)(quad * 32) << 16) + acc * (kMSub * kBN) + sub * kBN;
@@ -264,10 +265,10 @@ fwd_tc05_doc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_const
         float sum = run;
 #pragma unroll
         for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
-        if (ok && q_ok) {
-          const int64_t pair = (int64_t)q * P.Nb + d;
-          if (ARGMAX) P.argmax[pair * kLq + lane] = idx;
-          if (lane == 0) P.scores[pair] = sum;
+        if (q_ok) {
+          const int64_t pair = (int64_t)q * P.out_ld + P.out_col0 + d;
+          if (ARGMAX) P.argmax[pair * kLq + lane] = ok ? idx : 0;
+          if (lane == 0) P.scores[pair] = ok ? sum : __int_as_float(0x7fc00000);
         }
         dbeg = dend;
       }

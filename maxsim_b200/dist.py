@@ -10,22 +10,33 @@ Rerank (padded / packed candidates)
     :func:`score_candidates_padded_sharded`).
 
 Contrastive training
-    Rank r owns ``Nq/R`` queries and ``Nb/R`` documents.  Forward: the packed
-    document shards are all-gathered.  They are ragged, so each is padded to a
-    common row count for the collective; the gathered buffer is never
-    compacted -- it is handed to the operator as one packed tensor in which
-    every rank's padding rows form one filler document whose score column is
-    dropped.  One forward launch therefore scores the rank's queries against
-    all documents.  Backward: one launch routes the gradient; the partial
-    ``grad_documents`` of the whole buffer is reduce-scattered so each owner
-    receives the sum for its shard; ``grad_queries`` stays local.  Scores come
-    back as ``[Nq_local, Nb_total]`` with document columns in rank order, so
-    diagonal targets are ``rank_query_offset + arange(Nq_local)``
-    (:func:`score_contrastive_sharded`).
+    Rank r owns ``Nq/R`` queries and ``Nb/R`` documents.
+
+    Forward: the packed document shards (ragged) are all-gathered straight
+    into one packed buffer ``[T_total, D]`` in rank order -- no padding rows,
+    no compaction -- together with their lengths.  While that exchange runs,
+    the rank's queries are already scored against its OWN documents; the
+    remaining column blocks follow when the buffer is complete.  All launches
+    write into one ``[Nq_local, Nb_total]`` score matrix (document columns in
+    rank order, so diagonal targets are ``rank_query_offset + arange``).
+
+    Backward, ``exchange="owner"`` (default): ``grad_queries`` is computed
+    where the queries are.  For ``grad_documents`` one kernel regroups the
+    pairs' records -- the Lq winning tokens and the score gradient -- by
+    owning rank, one all-to-all delivers every owner the records of its
+    documents from all ranks (while ``grad_queries`` is being computed), the
+    queries were all-gathered during the forward pass, and each owner computes
+    the gradient of its own documents from all queries.  4 (Lq + 1) bytes per
+    pair cross the links instead of 4 D bytes per document token per rank.
+
+    ``exchange="reduce_scatter"``: every rank routes a partial
+    ``grad_documents`` for the whole buffer and the sums are reduce-scattered.
 
 Both drivers take the operator namespace as a parameter so that their
 sharding / reassembly logic can be exercised on CPU ``gloo`` ranks with a
-stand-in scorer; the default is the CUDA library.
+stand-in scorer; the default is the CUDA library, whose extra entry points
+(column blocks of a score matrix, record packing, gradients from records) are
+used when the namespace has them.
 """
 
 from __future__ import annotations
@@ -59,8 +70,14 @@ def _default_ops():
     import types
 
     from . import _ops
-    return types.SimpleNamespace(**vars(_ops.ops),
-                                 contrastive_backward_part=_ops.contrastive_backward_part)
+    return types.SimpleNamespace(
+        **vars(_ops.ops),
+        contrastive_backward_part=_ops.contrastive_backward_part,
+        contrastive_backward_native=_ops.contrastive_backward_native,
+        contrastive_forward_block=_ops.contrastive_forward_block,
+        pack_owner_records=_ops.pack_owner_records,
+        contrastive_backward_documents_from_records=_ops.contrastive_backward_documents_from_records,
+        offsets_from_lengths=lambda lengths: _ops.offsets_from_lengths(lengths, 2 ** 31 - 1)[0])
 
 
 def _world(group) -> Tuple[int, int]:
@@ -101,124 +118,83 @@ def score_candidates_padded_sharded(queries, documents, query_lengths, doc_lengt
 # Contrastive training: all-gather documents, per-owner gradient reduction
 # ---------------------------------------------------------------------------
 
-def _gather_shards(documents: torch.Tensor, lengths: torch.Tensor, group, world: int,
-                   n_queries: int = 0, shard_sizes=None):
-    """All-gather ragged packed shards into one buffer.
+class _Done:
+    """Stands in for the handle of an exchange that has already completed."""
 
-    Every shard is padded to ``t_pad = longest shard + 1`` token rows, so the
-    gathered buffer ``[world * t_pad, D]`` holds rank r's tokens at rows
-    ``[r * t_pad, r * t_pad + T_r)`` followed by at least one padding row.  The
-    buffer is then described to the operators as ONE packed document tensor:
-    rank r's real documents followed by one filler document that covers its
-    padding rows.  Returns the buffer, the combined int32 offsets, the column
-    indices of the real (non-filler) documents, the number of columns, the
-    per-rank ``(tokens, documents, queries)`` sizes and ``t_pad``."""
-    dev = documents.device
-    nccl = dist.get_backend(group) == "nccl"
+    def wait(self):
+        return True
+
+
+def _exchange_sizes(documents, lengths, n_queries, group, world, shard_sizes):
+    """Every rank's ``(document tokens, documents, queries)`` in rank order."""
     if shard_sizes is not None:
-        # the caller already knows every rank's (tokens, documents, queries): no
-        # exchange and, above all, no wait for the device on the host
+        # the caller already knows them: no exchange and, above all, no wait for
+        # the device on the host
         sizes = [(int(t), int(n), int(nq)) for t, n, nq in shard_sizes]
         rank = dist.get_rank(group)
-        if len(sizes) != world or sizes[rank] != (documents.shape[0], lengths.numel(), n_queries):
+        mine = (documents.shape[0], lengths.numel(), n_queries)
+        if len(sizes) != world or sizes[rank] != mine:
             raise ValueError(f"shard_sizes[{rank}] = {sizes[rank] if len(sizes) == world else None} does not "
-                             f"describe this rank's shard {(documents.shape[0], lengths.numel(), n_queries)}")
+                             f"describe this rank's shard {mine}")
+        return sizes
+    dev = documents.device
+    meta = torch.tensor([documents.shape[0], lengths.numel(), n_queries], dtype=torch.int64, device=dev)
+    metas = torch.empty((world, 3), dtype=torch.int64, device=dev)
+    if dist.get_backend(group) == "nccl":
+        dist.all_gather_into_tensor(metas, meta, group=group)
     else:
-        meta = torch.tensor([documents.shape[0], lengths.numel(), n_queries], dtype=torch.int64, device=dev)
-        metas = torch.empty((world, 3), dtype=torch.int64, device=dev)
-        if nccl:
-            dist.all_gather_into_tensor(metas, meta, group=group)
-        else:
-            dist.all_gather(list(metas.unbind(0)), meta, group=group)
-        sizes = [(int(t), int(n), int(nq)) for t, n, nq in metas.tolist()]  # one transfer for all ranks
-    t_pad = max(s[0] for s in sizes) + 1
-    n_max = max(s[1] for s in sizes)
+        dist.all_gather(list(metas.unbind(0)), meta, group=group)
+    return [(int(t), int(n), int(nq)) for t, n, nq in metas.tolist()]  # one transfer for all ranks
 
-    doc_pad = documents.new_zeros((t_pad, documents.shape[1]))
-    doc_pad[: documents.shape[0]] = documents
-    doc_parts = torch.empty((world * t_pad, documents.shape[1]), dtype=documents.dtype, device=dev)
-    if nccl:
-        handle = dist.all_gather_into_tensor(doc_parts, doc_pad, group=group, async_op=True)
-    else:
-        handle = dist.all_gather(list(doc_parts.view(world, t_pad, -1).unbind(0)), doc_pad,
-                                 group=group, async_op=True)
 
-    len_pad = torch.zeros(n_max, dtype=torch.int32, device=dev)
-    len_pad[: lengths.numel()] = lengths.to(torch.int32)
-    len_all = torch.empty((world, n_max), dtype=torch.int32, device=dev)
-    if nccl:
-        dist.all_gather_into_tensor(len_all, len_pad, group=group)
-    else:
-        dist.all_gather(list(len_all.unbind(0)), len_pad, group=group)
-    len_parts = len_all.unbind(0)
-
-    # combined document list: real documents of rank r, then its filler.  The
-    # column indices of the real documents are built on the host (the sizes are
-    # already there), so selecting them later needs no device synchronisation.
-    fillers = torch.tensor([t_pad - s[0] for s in sizes], dtype=torch.int32).to(dev, non_blocking=True)
-    pieces, real_cols, base = [], [], 0
+def _all_gather_rows(out: torch.Tensor, local: torch.Tensor, counts: Sequence[int], group, rank: int):
+    """Start gathering every rank's ``local [counts[r], ...]`` into ``out
+    [sum(counts), ...]`` in rank order; returns a handle to ``wait()`` on.  The
+    pieces land in place: ragged shards need neither padding nor compaction."""
+    views = list(out.split(list(counts), dim=0))
+    local = local.contiguous()
+    if dist.get_backend(group) == "nccl":
+        if all(c == counts[0] for c in counts):
+            return dist.all_gather_into_tensor(out, local, group=group, async_op=True)
+        return dist.all_gather(views, local, group=group, async_op=True)  # uneven pieces are supported
+    if all(c == counts[0] for c in counts):
+        return dist.all_gather(views, local, group=group, async_op=True)
+    # backends whose all-gather wants equal pieces: one broadcast per rank
+    world = len(counts)
     for r in range(world):
-        n_r = sizes[r][1]
-        pieces.append(len_parts[r][:n_r])
-        pieces.append(fillers[r:r + 1])
-        real_cols.extend(range(base, base + n_r))
-        base += n_r + 1
-    offsets = offsets_from_lengths(torch.cat(pieces))
-    real = torch.tensor(real_cols, dtype=torch.int64).to(dev, non_blocking=True)
-    handle.wait()
-    return doc_parts, offsets, real, base, sizes, t_pad
+        if r == rank:
+            views[r].copy_(local)
+        if counts[r]:
+            dist.broadcast(views[r], src=dist.get_global_rank(group, r) if group is not None else r,
+                           group=group)
+    return _Done()
 
 
-def _reduce_scatter_rows(full: torch.Tensor, world: int, rank: int, group) -> torch.Tensor:
-    """Sum ``full [world * t_pad, D]`` over the ranks and return this rank's
-    ``[t_pad, D]`` block.  NCCL does it in one reduce-scatter; backends without
-    one (gloo, used by the CPU tests) all-reduce and slice."""
-    t_pad = full.shape[0] // world
-    if dist.get_backend(group) == "nccl":
-        out = torch.empty((t_pad, full.shape[1]), dtype=full.dtype, device=full.device)
-        dist.reduce_scatter_tensor(out, full, group=group)
-        return out
-    dist.all_reduce(full, group=group)
-    return full[rank * t_pad:(rank + 1) * t_pad]
-
-
-def _all_gather_rows(x: torch.Tensor, rows_per_rank: Sequence[int], group, world: int) -> torch.Tensor:
-    """Concatenate every rank's ``x [rows_r, ...]`` along dim 0 (``rows_r`` may differ)."""
-    n_max = max(rows_per_rank)
-    pad = x
-    if x.shape[0] != n_max:
-        pad = x.new_zeros((n_max,) + tuple(x.shape[1:]))
-        pad[: x.shape[0]] = x
-    out = torch.empty((world * n_max,) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
-    if dist.get_backend(group) == "nccl":
-        dist.all_gather_into_tensor(out, pad.contiguous(), group=group)
+def _reduce_scatter_rows(full: torch.Tensor, counts: Sequence[int], rank: int, group) -> torch.Tensor:
+    """Sum ``full [sum(counts), D]`` over the ranks and return this rank's rows
+    ``[counts[rank], D]``.  NCCL reduce-scatters (ragged shards through a padded
+    copy); backends without a reduce-scatter (gloo, used by the CPU tests)
+    all-reduce and slice."""
+    world = len(counts)
+    begin = sum(counts[:rank])
+    if dist.get_backend(group) != "nccl":
+        dist.all_reduce(full, group=group)
+        return full[begin:begin + counts[rank]].contiguous()
+    t_max = max(counts)
+    if all(c == t_max for c in counts):
+        src = full
     else:
-        dist.all_gather(list(out.view((world, n_max) + tuple(x.shape[1:])).unbind(0)), pad.contiguous(),
-                        group=group)
-    if all(n == n_max for n in rows_per_rank):
-        return out
-    parts = out.view((world, n_max) + tuple(x.shape[1:]))
-    return torch.cat([parts[r, : rows_per_rank[r]] for r in range(world)], dim=0)
+        src = full.new_zeros((world * t_max, full.shape[1]))
+        for r, piece in enumerate(full.split(list(counts), dim=0)):
+            src[r * t_max:r * t_max + counts[r]].copy_(piece)
+    out = torch.empty((t_max, full.shape[1]), dtype=full.dtype, device=full.device)
+    dist.reduce_scatter_tensor(out, src, group=group)
+    return out[:counts[rank]].contiguous() if counts[rank] != t_max else out
 
 
-def _columns_to_owners(x: torch.Tensor, docs_per_rank: Sequence[int], queries_per_rank: Sequence[int],
-                       rank: int, group) -> torch.Tensor:
-    """``x [Nq_local, Nb_total, W]`` holds, for this rank's queries, one record
-    of W ints per document column (columns in rank order).  Every owner gets
-    the records of its own documents from all ranks: returns
-    ``[Nq_total, Nb_own, W]`` with queries in rank order."""
-    nq_local, _, width = x.shape
-    send = x.transpose(0, 1).contiguous().view(-1)                 # [Nb_total, Nq_local, W]
-    in_splits = [n * nq_local * width for n in docs_per_rank]
-    n_own = docs_per_rank[rank]
-    out_splits = [n_own * nq * width for nq in queries_per_rank]
-    recv = torch.empty((sum(out_splits),), dtype=x.dtype, device=x.device)
-    dist.all_to_all_single(recv, send, out_splits, in_splits, group=group)
-    blocks, at = [], 0
-    for nq, n in zip(queries_per_rank, out_splits):
-        blocks.append(recv[at:at + n].view(n_own, nq, width).transpose(0, 1))
-        at += n
-    return torch.cat(blocks, dim=0).contiguous()
+def _offsets(ops, lengths: torch.Tensor) -> torch.Tensor:
+    fn = getattr(ops, "offsets_from_lengths", None)
+    return fn(lengths) if fn is not None and lengths.is_cuda else offsets_from_lengths(lengths)
 
 
 class _ShardedContrastive(torch.autograd.Function):
@@ -228,63 +204,112 @@ class _ShardedContrastive(torch.autograd.Function):
         q = queries.contiguous()
         d_local = documents.contiguous()
         lens_local = doc_lengths.to(torch.int32).contiguous()
-        sizes = None
+        ctx.group, ctx.ops, ctx.rank, ctx.world, ctx.exchange = group, ops, rank, world, exchange
         if world == 1:
-            docs_all, offsets, real, n_cols = d_local, offsets_from_lengths(lens_local), None, 0
-            t_pad = d_local.shape[0]
+            offsets = _offsets(ops, lens_local)
+            scores, argmax = ops.maxsim_contrastive_forward_with_argmax(q, d_local, offsets)
+            ctx.save_for_backward(q, d_local, offsets, argmax)
+            return scores
+        dev = q.device
+        sizes = _exchange_sizes(d_local, lens_local, q.shape[0], group, world, shard_sizes)
+        tokens = [s[0] for s in sizes]
+        n_docs = [s[1] for s in sizes]
+        n_queries = [s[2] for s in sizes]
+        col0 = [sum(n_docs[:r]) for r in range(world + 1)]
+        nb_total, t_total = col0[-1], sum(tokens)
+
+        # start the exchanges: documents, their lengths and (for the owner exchange of the
+        # backward pass) the queries
+        docs_all = torch.empty((t_total, d_local.shape[1]), dtype=d_local.dtype, device=dev)
+        lens_all = torch.empty((nb_total,), dtype=torch.int32, device=dev)
+        h_lens = _all_gather_rows(lens_all, lens_local, n_docs, group, rank)
+        h_docs = _all_gather_rows(docs_all, d_local, tokens, group, rank)
+        q_all, h_q = None, None
+        if exchange == "owner":
+            q_all = torch.empty((sum(n_queries),) + tuple(q.shape[1:]), dtype=q.dtype, device=dev)
+            h_q = _all_gather_rows(q_all, q, n_queries, group, rank)
+
+        # this rank's own documents are scored while the exchange runs
+        block = getattr(ops, "contrastive_forward_block", None)
+        off_local = _offsets(ops, lens_local)
+        scores = argmax = None
+        if block is not None and q.is_cuda:
+            scores = torch.empty((q.shape[0], nb_total), dtype=torch.float32, device=dev)
+            argmax = torch.empty((q.shape[0], nb_total, q.shape[1]), dtype=torch.int32, device=dev)
+            if not block(q, d_local, off_local, scores, argmax, col0[rank], tokens[rank]):
+                scores = argmax = None  # shape outside the kernel: one ordinary call below
+        h_lens.wait()
+        h_docs.wait()
+        offsets = _offsets(ops, lens_all)
+        if scores is None:
+            scores, argmax = ops.maxsim_contrastive_forward_with_argmax(q, docs_all, offsets)
         else:
-            docs_all, offsets, real, n_cols, sizes, t_pad = _gather_shards(
-                d_local, lens_local, group, world, n_queries=q.shape[0], shard_sizes=shard_sizes)
-        scores_all, argmax = ops.maxsim_contrastive_forward_with_argmax(q, docs_all, offsets)
-        ctx.save_for_backward(q, docs_all, offsets, argmax, d_local, lens_local)
-        ctx.real, ctx.n_cols, ctx.sizes = real, n_cols, sizes
-        ctx.group, ctx.ops, ctx.rank, ctx.world = group, ops, rank, world
-        ctx.t_local, ctx.t_pad, ctx.exchange = d_local.shape[0], t_pad, exchange
-        return scores_all if real is None else scores_all.index_select(1, real)
+            for c_lo, c_hi in ((0, col0[rank]), (col0[rank + 1], nb_total)):
+                if c_hi > c_lo:
+                    n_tok = sum(tokens[r] for r in range(world) if c_lo <= col0[r] < c_hi)
+                    block(q, docs_all, offsets[c_lo:c_hi + 1], scores, argmax, c_lo, n_tok)
+        ctx.save_for_backward(q, docs_all, offsets, argmax, d_local, off_local)
+        ctx.q_all, ctx.h_q = q_all, h_q
+        ctx.tokens, ctx.n_docs, ctx.n_queries, ctx.col0 = tokens, n_docs, n_queries, col0
+        return scores
 
     @staticmethod
     def backward(ctx, dscore):
-        q, docs_all, offsets, argmax, d_local, lens_local = ctx.saved_tensors
         ops, group, rank, world = ctx.ops, ctx.group, ctx.rank, ctx.world
-        part = getattr(ops, "contrastive_backward_part", None)
         g = dscore.contiguous().to(torch.float32)
+        none5 = (None,) * 5
         if world == 1:
-            dq, dd_all = ops.maxsim_contrastive_backward(g, q, docs_all, offsets, argmax)
-            return dq, dd_all, None, None, None, None, None
-        # filler documents receive no gradient
-        g_all = torch.zeros((g.shape[0], ctx.n_cols), dtype=torch.float32, device=g.device)
-        g_all.index_copy_(1, ctx.real, g)
-
+            q, d_local, offsets, argmax = ctx.saved_tensors
+            dq, dd = ops.maxsim_contrastive_backward(g, q, d_local, offsets, argmax)
+            return (dq, dd) + none5
+        q, docs_all, offsets, argmax, d_local, off_local = ctx.saved_tensors
         if ctx.exchange == "reduce_scatter":
-            dq, dd_all = ops.maxsim_contrastive_backward(g_all, q, docs_all, offsets, argmax)
-            mine = _reduce_scatter_rows(dd_all, world, rank, group)
-            return dq, mine[: ctx.t_local].contiguous(), None, None, None, None, None
+            dq, dd_all = ops.maxsim_contrastive_backward(g, q, docs_all, offsets, argmax)
+            return (dq, _reduce_scatter_rows(dd_all, ctx.tokens, rank, group)) + none5
 
-        # "owner": grad_queries is computed here, where the queries are.  For
-        # grad_documents every rank sends each owner the argmax and the score
-        # gradient of that owner's documents (one int32 record of Lq + 1 words
-        # per pair) and the queries are all-gathered; each owner then computes
-        # the gradient of its own documents from all queries.  This moves
-        # 4 * (Lq + 1) bytes per pair instead of 4 * dim bytes per document
-        # token per rank, and no partial sums.
-        if part is not None:
-            dq = part(g_all, q, docs_all, offsets, argmax, want_queries=True, want_documents=False)[0]
+        # "owner".  The records of this rank's pairs go to the owners of the documents ...
+        n_docs, n_queries, col0 = ctx.n_docs, ctx.n_queries, ctx.col0
+        nq_local, lq = q.shape[0], q.shape[1]
+        pack = getattr(ops, "pack_owner_records", None)
+        if pack is not None and g.is_cuda:
+            col_start = torch.tensor(col0, dtype=torch.int32).to(g.device, non_blocking=True)
+            send = pack(argmax, g, col_start)
         else:
-            dq = ops.maxsim_contrastive_backward(g_all, q, docs_all, offsets, argmax)[0]
-        docs_per_rank = [s[1] for s in ctx.sizes]
-        queries_per_rank = [s[2] for s in ctx.sizes]
-        record = torch.cat([argmax.index_select(1, ctx.real).to(torch.int32),
-                            g.view(torch.int32).unsqueeze(-1)], dim=2)      # [Nq_local, Nb_total, Lq + 1]
-        mine = _columns_to_owners(record, docs_per_rank, queries_per_rank, rank, group)
-        a_own = mine[:, :, :-1].contiguous()
-        g_own = mine[:, :, -1].contiguous().view(torch.float32)
-        q_all = _all_gather_rows(q, queries_per_rank, group, world)
-        off_local = offsets_from_lengths(lens_local)
-        if part is not None:
-            dd = part(g_own, q_all, d_local, off_local, a_own, want_queries=False, want_documents=True)[1]
-        else:
-            dd = ops.maxsim_contrastive_backward(g_own, q_all, d_local, off_local, a_own)[1]
-        return dq, dd, None, None, None, None, None
+            record = torch.cat([argmax.to(torch.int32), g.view(torch.int32).unsqueeze(-1)], dim=2)
+            send = torch.cat([record[:, col0[o]:col0[o + 1]].reshape(-1) for o in range(world)])
+        width = lq + 1
+        in_splits = [n * nq_local * width for n in n_docs]
+        out_splits = [n_docs[rank] * nq * width for nq in n_queries]
+        recv = torch.empty((sum(out_splits),), dtype=torch.int32, device=g.device)
+        h_rec = dist.all_to_all_single(recv, send, out_splits, in_splits, group=group, async_op=True)
+
+        # ... while grad_queries is computed here, where the queries are
+        native = getattr(ops, "contrastive_backward_native", None)
+        part = getattr(ops, "contrastive_backward_part", None)
+        dq = None
+        if native is not None:
+            got = native(g, q, docs_all, offsets, argmax, want_documents=False)
+            dq = got[0] if got is not None else None
+        if dq is None and part is not None:
+            dq = part(g, q, docs_all, offsets, argmax, want_queries=True, want_documents=False)[0]
+        if dq is None:
+            dq = ops.maxsim_contrastive_backward(g, q, docs_all, offsets, argmax)[0]
+
+        # every owner now holds [all queries, own documents, Lq + 1] and all queries
+        h_rec.wait()
+        ctx.h_q.wait()
+        q_all = ctx.q_all
+        from_records = getattr(ops, "contrastive_backward_documents_from_records", None)
+        dd = from_records(recv, q_all, d_local, off_local) if from_records is not None and g.is_cuda else None
+        if dd is None:
+            rec = recv.view(q_all.shape[0], n_docs[rank], width)
+            a_own = rec[:, :, :lq].contiguous()
+            g_own = rec[:, :, lq].contiguous().view(torch.float32)
+            if part is not None:
+                dd = part(g_own, q_all, d_local, off_local, a_own, want_queries=False, want_documents=True)[1]
+            else:
+                dd = ops.maxsim_contrastive_backward(g_own, q_all, d_local, off_local, a_own)[1]
+        return (dq, dd) + none5
 
 
 def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, ops=None,

@@ -85,6 +85,13 @@ class GraphedContrastiveStep:
                              f"got {tuple(documents.shape)}")
         if document_offsets.numel() != self.n_documents + 1:
             raise ValueError(f"document_offsets must have {self.n_documents + 1} elements")
+        if document_offsets.device.type == "cpu":
+            # offsets on the host cost nothing to check; device offsets are the caller's
+            # contract (first 0, strictly increasing, last == T), as for the C ABI
+            off = document_offsets.to(torch.int64)
+            if int(off[0]) != 0 or int(off[-1]) != T or bool((off[1:] <= off[:-1]).any()):
+                raise ValueError("document_offsets must start at 0, increase strictly and end at "
+                                 f"the token count {T}")
         with torch.no_grad():
             self._q.copy_(queries, non_blocking=True)
             self._d[:T].copy_(documents, non_blocking=True)

@@ -166,7 +166,9 @@ def score_candidates_padded_from_host(queries: torch.Tensor, documents: torch.Te
     from it, so padding rows never cross PCIe; a pageable ``documents`` is
     copied whole.  ``staging`` is the device-side ``[B, C, Ld, D]`` landing
     buffer (one is kept per batch shape when not given; its padding rows hold
-    whatever they held before, and no kernel reads them).
+    whatever they held before, and no kernel reads them).  The kept buffer is
+    shared by every call of that shape and is ordered only by the stream the
+    calls run on: callers that use several streams pass their own ``staging``.
 
     Returns the ``[B, C]`` fp32 scores on the host.  With a pinned ``out`` the
     copy back is asynchronous on the current stream of ``device`` and ``out``
@@ -180,6 +182,8 @@ def score_candidates_padded_from_host(queries: torch.Tensor, documents: torch.Te
     device = torch.device(device)
     if device.type != "cuda":
         raise RuntimeError(f"device must be a CUDA device (maxsim_b200 has no CPU path); got {device}")
+    if device.index is None:  # "cuda" means the current device; tensors report an index
+        device = torch.device("cuda", torch.cuda.current_device())
     documents = documents.contiguous()
     with torch.cuda.device(device):
         q = queries.contiguous().to(device, non_blocking=True)

@@ -173,6 +173,21 @@ def _device_unit_rows(n: int, dim: int, seed: int, device, dtype) -> torch.Tenso
     return x.to(dtype)
 
 
+def c3_shard_lengths(q_begin: int, q_end: int, *, seed: int = 2, Lq: int = 32, C: int = 1000,
+                     Ld: int = 300):
+    """``(query_lengths [n], doc_lengths [n, C])`` (int32 numpy) of queries
+    ``[q_begin, q_end)`` of the large rerank configuration: the lengths
+    :func:`c3_device_shard` generates, without touching a device."""
+    n = q_end - q_begin
+    qlen = np.empty((n,), dtype=np.int32)
+    dlen = np.empty((n, C), dtype=np.int32)
+    for i, qi in enumerate(range(q_begin, q_end)):
+        rng = np.random.default_rng([seed, qi])
+        dlen[i] = lognormal_lengths(rng, C, 180.0, 0.4, min(16, Ld), Ld)
+        qlen[i] = int(Lq - rng.integers(0, 5))
+    return qlen, dlen
+
+
 def c3_device_shard(q_begin: int, q_end: int, device, *, seed: int = 2, Lq: int = 32,
                     C: int = 1000, Ld: int = 300, dim: int = 128,
                     dtype: torch.dtype = torch.float16) -> Dict[str, torch.Tensor]:
@@ -182,12 +197,9 @@ def c3_device_shard(q_begin: int, q_end: int, device, *, seed: int = 2, Lq: int 
     n = q_end - q_begin
     queries = torch.empty((n, Lq, dim), device=device, dtype=dtype)
     documents = torch.empty((n, C, Ld, dim), device=device, dtype=dtype)
-    qlen = torch.empty((n,), dtype=torch.int32)
-    dlen = torch.empty((n, C), dtype=torch.int32)
+    qlen_np, dlen_np = c3_shard_lengths(q_begin, q_end, seed=seed, Lq=Lq, C=C, Ld=Ld)
+    qlen, dlen = torch.from_numpy(qlen_np), torch.from_numpy(dlen_np)
     for i, qi in enumerate(range(q_begin, q_end)):
-        rng = np.random.default_rng([seed, qi])
-        dlen[i] = torch.from_numpy(lognormal_lengths(rng, C, 180.0, 0.4, min(16, Ld), Ld))
-        qlen[i] = int(Lq - rng.integers(0, 5))
         s = (seed * 1_000_003 + qi) * 2 + 1
         queries[i] = _device_unit_rows(Lq, dim, s, device, dtype).view(Lq, dim)
         documents[i] = _device_unit_rows(C * Ld, dim, s + 1, device, dtype).view(C, Ld, dim)

@@ -13,7 +13,8 @@ import torch
 import maxsim_b200 as maxsim
 from maxsim_b200 import _ops
 from maxsim_b200 import workloads as W
-from _util import GOLDEN, assert_argmax, assert_grads, assert_scores, f32, i64, oracle
+from _util import (GOLDEN, assert_all_pairs, assert_argmax, assert_grads, assert_scores, f32,
+                   gpu_einsum_contrastive, gpu_einsum_padded, i64, oracle)
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -103,6 +104,29 @@ def test_config3_full_size_properties():
     assert torch.equal(shard["documents"], d[128:130]) and torch.equal(shard["doc_lengths"], dl[128:130])
 
 
+def test_config3_full_size_every_pair_against_fp32_einsum():
+    """All 256 000 pairs of the full-size rerank configuration, scores and
+    argmax, against the chunked fp32 einsum on the same device; the checker
+    itself is pinned to the CPU oracle on a few candidates first."""
+    free, _ = torch.cuda.mem_get_info()
+    if free < 45 * 2 ** 30:
+        pytest.skip("needs about 40 GB of free device memory")
+    data = W.c3_device_shard(0, 256, DEV)
+    q, d, ql, dl = data["queries"], data["documents"], data["query_lengths"], data["doc_lengths"]
+    cs, ca, cg = gpu_einsum_padded(q[:2], d[:2, :40], ql[:2], dl[:2, :40])
+    ws, wa, wg = oracle.score_candidates_padded(f32(q[:2]), f32(d[:2, :40]), i64(ql[:2]),
+                                                i64(dl[:2, :40]), want_gap=True)
+    assert_scores(f32(cs), ws, "fp32")
+    assert_argmax(ca.cpu().numpy(), wa, wg, "fp16")
+    s, a = maxsim.score_candidates_padded_with_argmax(q, d, ql, dl)
+    s_only = maxsim.score_candidates_padded(q, d, ql, dl)
+    assert torch.equal(s, s_only)
+    want_s, want_a, gaps = gpu_einsum_padded(q, d, ql, dl)
+    n_diff, max_err = assert_all_pairs(s, a, want_s, want_a, gaps, "fp16")
+    assert max_err < 1e-3
+    assert n_diff < 1e-3 * a.numel()
+
+
 def test_config4_packed_grid_fp16_forward_backward():
     wl = W.c4_packed_grid_fp16()
     q = W.to_torch(wl.queries, "fp16", DEV).requires_grad_(True)
@@ -119,13 +143,13 @@ def test_config4_packed_grid_fp16_forward_backward():
     s2, a = maxsim.score_pairs_packed_with_argmax(q.detach(), qo, d.detach(), do, pq, pd)
     assert a.shape == (65536, 32)
     qf, df = f32(q), f32(d)
-    # forward against the oracle on a strided subset of the pairs
-    sel = np.arange(0, 65536, 16)
+    # forward against the oracle on all 65 536 pairs
     ws, wa, gaps = oracle.score_pairs_packed(qf, wl.query_offsets, df, wl.document_offsets,
-                                             wl.pair_query_ids[sel], wl.pair_document_ids[sel],
+                                             wl.pair_query_ids, wl.pair_document_ids,
                                              max_q_len=32, want_gap=True)
-    assert_scores(f32(s2)[sel], ws, "fp16")
-    assert_argmax(a.cpu().numpy()[sel], wa, gaps, "fp16")
+    assert_scores(f32(s2), ws, "fp16")
+    assert_scores(f32(s), ws, "fp16", "scores(train)")
+    assert_argmax(a.cpu().numpy(), wa, gaps, "fp16")
     # backward against the oracle on all pairs (routing through the kernel's argmax)
     wq, wd = oracle.pairs_packed_backward(wl.dscore, qf, wl.query_offsets, df, wl.document_offsets,
                                           wl.pair_query_ids, wl.pair_document_ids, a.cpu().numpy())
@@ -184,3 +208,39 @@ def test_config5_full_size_properties():
     rhs = float((g * s).sum())
     assert abs(lhs - rhs) <= 2e-3 * abs(rhs) + 1.0
     assert abs(mid - rhs) <= 2e-3 * abs(rhs) + 1.0
+
+
+def test_config5_full_size_every_pair_against_fp32_einsum():
+    """All 1 048 576 pairs of the full-size ties configuration, scores and
+    argmax, against the chunked fp32 einsum on the same device (pinned to the
+    CPU oracle on a block of queries first), for both tilings of the tcgen05
+    kernel; duplicated tokens (exact ties in the checker) must give the first
+    index everywhere."""
+    data = W.c5_device(DEV)
+    q, d, off = data["queries"], data["documents"], data["document_offsets"]
+    want_s, want_a, gaps = gpu_einsum_contrastive(q, d, off)
+    ws, wa, wg = oracle.score_contrastive(f32(q[:4]), f32(d), i64(off), want_gap=True)
+    assert_scores(f32(want_s[:4]), ws, "fp32")
+    assert_argmax(want_a[:4].cpu().numpy(), wa, wg, "bf16")
+    exact = gaps == 0
+    assert float(exact.float().mean()) > 0.01
+    for path in (8, 9):
+        _ops.set_forward_path(path)
+        s, a = maxsim.score_contrastive_with_argmax(q, d, off)
+        n_diff, max_err = assert_all_pairs(s, a, want_s, want_a, gaps, "bf16")
+        assert max_err < 2e-3 and n_diff < 1e-3 * a.numel()
+        # A tie of the checker is either a duplicated token (identical rows: the first copy
+        # has to win in any arithmetic) or, a few times in 33 million, two different tokens
+        # whose fp32 sums happen to coincide in the checker's summation order.
+        mism = exact & (a != want_a)
+        if bool(mism.any()):
+            _, d_idx, _ = mism.nonzero(as_tuple=True)
+            base = off.to(torch.int64)[d_idx]
+            got_rows = d[base + a[mism].to(torch.int64)]
+            want_rows = d[base + want_a[mism].to(torch.int64)]
+            duplicated = (got_rows == want_rows).all(dim=1)
+            assert not bool(duplicated.any()), "a duplicated token did not give its first copy"
+            assert int(mism.sum()) < 1e-5 * a.numel()
+    _ops.set_forward_path(0)
+    s_only = maxsim.score_contrastive(q, d, off)
+    torch.testing.assert_close(s_only, want_s, rtol=1e-4, atol=1e-3)

@@ -77,6 +77,52 @@ def test_contrastive_train_step_replays_from_a_graph():
     assert _ops.device_status() == 0
 
 
+def test_packed_train_step_in_a_graph_follows_new_pair_ids():
+    """The grouping of the pair list (by document and by query) must be part of
+    the captured work: a replay after the id tensors were overwritten has to
+    route the gradients of the NEW pairs."""
+    from maxsim_b200 import workloads as W
+    wl = W.c4_packed_grid_fp16(seed=9, n_queries=60, n_docs=200, n_pairs=4096, dim=96)
+    assert wl.pair_query_ids.shape[0] >= _ops.GROUP_MIN_PAIRS
+    q = W.to_torch(wl.queries, "fp16", DEV).requires_grad_(True)
+    d = W.to_torch(wl.documents, "fp16", DEV).requires_grad_(True)
+    qo = torch.from_numpy(wl.query_offsets).to(DEV)
+    do = torch.from_numpy(wl.document_offsets).to(DEV)
+    pq = torch.from_numpy(wl.pair_query_ids).to(DEV)
+    pd = torch.from_numpy(wl.pair_document_ids).to(DEV)
+    w = torch.from_numpy(wl.dscore).to(DEV)
+
+    def step():
+        s = maxsim.score_pairs_packed_train(q, qo, d, do, pq, pd, max_q_len=32)
+        gq, gd = torch.autograd.grad(s, (q, d), w)
+        return s, gq, gd
+
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            step()
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        s, gq, gd = step()
+    graph.replay()
+    torch.cuda.synchronize()
+    first = [t.detach().clone() for t in (s, gq, gd)]
+    # new pair lists in the same tensors (ids stay in range, so the layout stays valid)
+    gen = torch.Generator().manual_seed(3)
+    pq.copy_(torch.randint(0, 60, (4096,), generator=gen, dtype=torch.int32))
+    pd.copy_(torch.randint(0, 200, (4096,), generator=gen, dtype=torch.int32))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert not torch.equal(s, first[0])
+    want = [t.detach() for t in step()]
+    assert torch.equal(s, want[0])
+    torch.testing.assert_close(gq.float(), want[1].float(), rtol=2e-2, atol=1e-3)
+    torch.testing.assert_close(gd.float(), want[2].float(), rtol=2e-2, atol=1e-3)
+    assert _ops.device_status() == 0
+
+
 def test_graphed_contrastive_step_follows_batches_of_different_token_counts():
     torch.manual_seed(0)
     Nq, Lq, Nb, dim = 16, 32, 12, 128

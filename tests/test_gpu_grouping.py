@@ -137,12 +137,25 @@ def test_order_follows_an_in_place_change_of_the_pair_list():
     wl = _wl(3000)
     q, qo, d, do, pq, pd = _dev(wl)
     s0 = maxsim.score_pairs_packed(q, qo, d, do, pq, pd)
+    w = torch.randn(3000, device=DEV)
+
+    def grads():
+        qr, dr = q.clone().requires_grad_(True), d.clone().requires_grad_(True)
+        maxsim.score_pairs_packed_train(qr, qo, dr, do, pq, pd, max_q_len=32).backward(w)
+        return qr.grad.float(), dr.grad.float()
+
+    grads()  # builds and remembers the groupings of the current lists
     pd.copy_(pd.flip(0))
+    pq.copy_(pq.roll(7))
     s1 = maxsim.score_pairs_packed(q, qo, d, do, pq, pd)
+    gq1, gd1 = grads()  # the grouped backward has to follow the new lists
     _ops.set_pair_grouping(False)
     want = maxsim.score_pairs_packed(q, qo, d, do, pq, pd)
+    wq, wd = grads()
     assert torch.equal(s1, want)
     assert not torch.equal(s0, s1)
+    torch.testing.assert_close(gq1, wq, rtol=2e-2, atol=1e-3)
+    torch.testing.assert_close(gd1, wd, rtol=2e-2, atol=1e-3)
 
 
 def test_int64_pair_ids_and_short_lists():

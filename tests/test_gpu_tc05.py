@@ -1,7 +1,8 @@
-"""The tcgen05 / TMEM contrastive forward (queries [Nq, 32, 128], fp16 / bf16)
-against the oracle and against the streaming kernel: document boundaries at
-every position relative to the 128-token tiles and the 32-column chunks,
-partial query groups, exact ties, non-finite inputs."""
+"""The tcgen05 / TMEM contrastive forward (fp16 / bf16, Lq <= 64, dim a multiple
+of 16 up to 128) against the oracle and against the streaming kernel: document
+boundaries at every position relative to the 128-token tiles and the 16-column
+groups of the fold, partial query groups, every lanes-per-query setting, exact
+ties, maxima that take the exact walk (negative, large, non-finite)."""
 
 from __future__ import annotations
 
@@ -26,10 +27,10 @@ def _force_tc05():
     assert _ops.device_status() == 0, "a bounded wait ran out"
 
 
-def _make(Nq, d_lens, dtype, seed):
+def _make(Nq, d_lens, dtype, seed, Lq=32, dim=128, scale=1.0):
     g = torch.Generator().manual_seed(seed)
-    q = torch.randn(Nq, 32, 128, generator=g).to(DEV, dtype)
-    d = torch.randn(sum(d_lens), 128, generator=g).to(DEV, dtype)
+    q = (scale * torch.randn(Nq, Lq, dim, generator=g)).to(DEV, dtype)
+    d = torch.randn(sum(d_lens), dim, generator=g).to(DEV, dtype)
     off = torch.zeros(len(d_lens) + 1, dtype=torch.int32)
     off[1:] = torch.tensor(d_lens, dtype=torch.int32).cumsum(0)
     return q, d, off.to(DEV)
@@ -56,14 +57,52 @@ SHAPES = [
 
 @pytest.mark.parametrize("Nq,d_lens", SHAPES)
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-# 3: default, 5: M = 512 / 64-token tiles, 6: two CTAs per SM, 7: the earlier epilogue (no
-# register hand-over, full-width argmax search), 8: tiles that start at document starts,
-# 9: tiles that ignore document boundaries (3 chooses between 8 and 9 by document length)
-@pytest.mark.parametrize("path", [3, 5, 6, 7, 8, 9])
+# 3: tcgen05 kernel with the tiling chosen by document length, 8: every document tiled on
+# its own, 9: 128-token tiles that ignore document boundaries
+@pytest.mark.parametrize("path", [3, 8, 9])
 def test_tc05_matches_oracle(Nq, d_lens, dtype, path):
     _ops.set_forward_path(path)
     q, d, off = _make(Nq, d_lens, dtype, 11)
     _check(q, d, off, dtype)
+
+
+# query lengths on 16, 32 and 64 accumulator lanes (exact fits and zero-filled rows) and
+# every dim the operand boxes cover (one box, a zero-filled second box, two boxes)
+@pytest.mark.parametrize("Lq,dim", [(16, 128), (7, 64), (20, 96), (32, 64), (32, 96), (32, 16),
+                                    (48, 128), (64, 128), (64, 96), (33, 48), (1, 32)])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("path", [8, 9])
+def test_tc05_query_lengths_and_dims(Lq, dim, dtype, path):
+    _ops.set_forward_path(path)
+    for Nq, d_lens in ((16, [31, 200, 128, 5, 129, 64, 1, 300]), (37, [90] * 9 + [17])):
+        q, d, off = _make(Nq, d_lens, dtype, 17 + Lq, Lq=Lq, dim=dim)
+        _check(q, d, off, dtype)
+
+
+@pytest.mark.parametrize("path", [8, 9])
+@pytest.mark.parametrize("Lq", [16, 32, 64])
+def test_tc05_large_and_negative_maxima_take_the_exact_walk(path, Lq):
+    _ops.set_forward_path(path)
+    # similarities of magnitude well above 64: compared exactly, first index wins
+    q, d, off = _make(16, [150, 40, 129, 256, 3], torch.bfloat16, 31, Lq=Lq, scale=8.0)
+    s, a = _check(q, d, off, torch.bfloat16)
+    assert float(s.abs().max()) > 64 * Lq / 4
+    # every similarity negative: documents are copies of -q direction mixtures
+    g = torch.Generator().manual_seed(5)
+    base = torch.randn(1, 128, generator=g)
+    qn = (base + 0.05 * torch.randn(16, Lq, 128, generator=g)).to(DEV, torch.float16)
+    dn = (-base + 0.05 * torch.randn(400, 128, generator=g)).to(DEV, torch.float16)
+    offn = torch.tensor([0, 130, 131, 300, 400], dtype=torch.int32, device=DEV)
+    s, a = _check(qn, dn, offn, torch.float16)
+    assert float(s.max()) < 0
+    # duplicated tokens with a negative maximum: the first copy wins
+    dn2 = dn.clone()
+    dn2[200:300] = dn2[131:132]
+    _, a2 = maxsim.score_contrastive_with_argmax(qn[:, :, :], dn2[131:300].contiguous(),
+                                                 torch.tensor([0, 169], dtype=torch.int32, device=DEV))
+    ws, wa, gaps = oracle.score_contrastive(f32(qn), f32(dn2[131:300]), np.array([0, 169]), want_gap=True)
+    exact = gaps == 0
+    assert np.array_equal(a2.cpu().numpy()[exact], wa[exact])
 
 
 def test_tc05_agrees_with_streaming_kernel_bitwise_on_argmax():
@@ -76,7 +115,7 @@ def test_tc05_agrees_with_streaming_kernel_bitwise_on_argmax():
     assert (a_tc != a_mma).float().mean() < 1e-3
 
 
-@pytest.mark.parametrize("path", [7, 8, 9])
+@pytest.mark.parametrize("path", [8, 9])
 def test_tc05_exact_ties_and_duplicated_tokens(path):
     _ops.set_forward_path(path)
     wl = W.c5_contrastive_ties_bf16(seed=21, Nq=16, Nb=24, lo=20, hi=300, dup_frac=0.1)
@@ -99,7 +138,7 @@ def test_tc05_exact_ties_and_duplicated_tokens(path):
     assert (a2 == 0).all()
 
 
-@pytest.mark.parametrize("path", [7, 8, 9])
+@pytest.mark.parametrize("path", [8, 9])
 def test_tc05_non_finite_contract(path):
     _ops.set_forward_path(path)
     q, d, off = _make(16, [64, 200, 33], torch.float16, 13)
