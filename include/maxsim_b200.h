@@ -66,6 +66,13 @@ MAXSIM_API const char* maxsim_b200_last_error(void);
 /* Synchronises `stream`, then returns and clears the device-side status word
  * that kernels set when one of their bounded waits gave up (0 = clean). */
 MAXSIM_API int maxsim_b200_device_status(void* stream);
+/* Exercises the time-out reporting path without putting anything at risk
+ * (no reference counterpart): one thread waits `polls` polls (1 .. 2^20) on a
+ * barrier nothing arrives at, through the same bounded wait the tensor-core
+ * kernels use, gives up, sets the status bit maxsim_b200_device_status
+ * reports and writes 1 to *gave_up (device memory, may be NULL).  No copy or
+ * MMA is in flight in that kernel, so the device is clean afterwards. */
+MAXSIM_API int maxsim_b200_wait_probe(int64_t polls, int* gave_up, void* stream);
 /* Number of kernel launches this process has enqueued through the library. */
 MAXSIM_API int64_t maxsim_b200_launch_count(void);
 /* Selects the forward implementation: 0 = automatic, 1 = force the portable
@@ -363,6 +370,24 @@ MAXSIM_API int maxsim_contrastive_backward(
     float* grad_queries, float* grad_documents,
     int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim,
     int64_t total_d_tokens, int dtype, void* stream);
+
+/* As maxsim_packed_backward_grouped with both gradients written once in the
+ * inputs' float16 / bfloat16 type (what autograd's cast of the float gradients
+ * gives, without the float tensors and the cast's pass over them; reference
+ * behaviour replaced: torch-ext/maxsim/__init__.py:448-454 after
+ * maxsim_cuda/maxsim.cu:2251-2252).  Needs the four grouping arrays, dim % 8 ==
+ * 0, dim <= 128; MAXSIM_EUNSUPPORTED otherwise.  A document with more than 512
+ * routed terms is summed in batches with one extra rounding per batch. */
+MAXSIM_API int maxsim_packed_backward_grouped_native(
+    const float* dscore, const void* queries, const int32_t* query_offsets,
+    const void* documents, const int32_t* document_offsets,
+    const int32_t* pair_query_ids, const int32_t* pair_document_ids,
+    const int32_t* order_by_query, const int32_t* ends_by_query,
+    const int32_t* order_by_document, const int32_t* ends_by_document,
+    const int32_t* argmax, void* grad_queries, void* grad_documents,
+    int64_t n_pairs, int64_t n_queries, int64_t n_documents,
+    int64_t total_q_tokens, int64_t total_d_tokens,
+    int64_t dim, int64_t max_q_len, int dtype, void* stream);
 
 /* Gradients in the inputs' element type (no compiled reference counterpart:
  * the reference's operators return fp32 gradients, maxsim_cuda/maxsim.cu:

@@ -102,8 +102,10 @@ def score_pairs_packed_with_argmax(queries, query_offsets, documents, document_o
 
 class _PackedFn(torch.autograd.Function):
     """Forward saves the int32 argmax; backward routes the upstream gradient
-    through it.  Gradients come back as fp32 (autograd casts them to the leaf
-    dtype), as in torch-ext/maxsim/__init__.py:414-454."""
+    through it.  The operator returns fp32 gradients that autograd casts to the
+    leaf dtype, as in torch-ext/maxsim/__init__.py:414-454; grouped lists of
+    float16 / bfloat16 tensors get them from the kernels in that dtype directly
+    (every row summed in fp32, rounded once)."""
 
     @staticmethod
     def forward(ctx, queries, query_offsets, documents, document_offsets,
@@ -120,7 +122,11 @@ class _PackedFn(torch.autograd.Function):
     def backward(ctx, dscore):
         q, qoff, d, doff, pq, pd, argmax = ctx.saved_tensors
         g = dscore.contiguous().to(torch.float32)
-        dq, dd = ops.maxsim_packed_backward(g, q, qoff, d, doff, pq, pd, argmax, ctx.max_q_len)
+        native = _ops.packed_backward_native(g, q, qoff, d, doff, pq, pd, argmax, ctx.max_q_len)
+        if native is not None:  # grouped list of 16-bit tensors: gradients already in the leaf dtype
+            dq, dd = native
+        else:
+            dq, dd = ops.maxsim_packed_backward(g, q, qoff, d, doff, pq, pd, argmax, ctx.max_q_len)
         return dq, None, dd, None, None, None, None
 
 

@@ -50,22 +50,33 @@ def is_current() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile the library if it is missing or older than its sources."""
+    """Compile the library if it is missing or older than its sources.  Several
+    processes may call this at once (one per GPU): the build runs under a file
+    lock, into a temporary name, and whoever comes second finds it done."""
     if not force and is_current():
         return LIB_PATH
     nvcc = _find_nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build libmaxsim_b200.so")
-    cmd = [nvcc, *NVCC_FLAGS]
-    if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB_PATH)] + [str(CSRC / s) for s in SOURCES]
-    proc = subprocess.run(cmd, capture_output=True, text=True)
-    if proc.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
-    if verbose:
-        sys.stderr.write(proc.stderr)
-    STAMP_PATH.write_text(source_digest() + "\n")
+    import fcntl
+
+    with open(PKG_DIR / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        if not force and is_current():
+            return LIB_PATH
+        tmp = LIB_PATH.with_suffix(f".so.tmp{os.getpid()}")
+        cmd = [nvcc, *NVCC_FLAGS]
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+        cmd += ["-o", str(tmp)] + [str(CSRC / s) for s in SOURCES]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            tmp.unlink(missing_ok=True)
+            raise RuntimeError("nvcc failed:\n" + proc.stdout + proc.stderr)
+        if verbose:
+            sys.stderr.write(proc.stderr)
+        os.replace(tmp, LIB_PATH)
+        STAMP_PATH.write_text(source_digest() + "\n")
     return LIB_PATH
 
 

@@ -39,6 +39,7 @@ _SIGNATURES = {
     "maxsim_b200_last_error": (c_char_p, []),
     "maxsim_b200_device_status": (c_int, [_P]),
     "maxsim_b200_launch_count": (c_int64, []),
+    "maxsim_b200_wait_probe": (c_int, [_I64, _P, _P]),
     "maxsim_b200_set_forward_path": (None, [c_int]),
     "maxsim_b200_layout_stats": (c_int, [_P, _I64, _P, _I64, c_int, _P, _P]),
     "maxsim_b200_contrastive_ce": (c_int, [_P] * 4 + [_I64] * 2 + [ctypes.c_float] * 2 + [_P]),
@@ -52,6 +53,7 @@ _SIGNATURES = {
     "maxsim_forward_ordered": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_forward_with_argmax_ordered": (c_int, [_P] * 9 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_backward_grouped": (c_int, [_P] * 14 + [_I64] * 7 + [c_int, _P]),
+    "maxsim_packed_backward_grouped_native": (c_int, [_P] * 14 + [_I64] * 7 + [c_int, _P]),
     "maxsim_forward": (c_int, [_P] * 7 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_forward_with_argmax": (c_int, [_P] * 8 + [_I64] * 7 + [c_int, _P]),
     "maxsim_packed_backward": (c_int, [_P] * 10 + [_I64] * 7 + [c_int, _P]),
@@ -114,6 +116,18 @@ def device_status(device=None) -> int:
     """Synchronise the current stream and return the kernels' status word."""
     with torch.cuda.device(device):
         return int(load_library().maxsim_b200_device_status(_stream_ptr()))
+
+
+def wait_probe(polls: int = 64, device=None) -> bool:
+    """Launch the kernel whose only wait cannot be satisfied (see the header):
+    returns True if it gave up after ``polls`` polls.  ``device_status()``
+    reports the time-out bit afterwards, and clears it."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    flag = torch.zeros((1,), dtype=torch.int32, device=dev)
+    with _on_device(dev):
+        rc = load_library().maxsim_b200_wait_probe(int(polls), flag.data_ptr(), _stream_ptr())
+    _check(rc, "maxsim_b200_wait_probe")
+    return bool(flag.item())
 
 
 def layout_stats(items) -> list:
@@ -499,6 +513,41 @@ def maxsim_packed_backward(dscore, queries, query_offsets, documents, document_o
             n_pairs, qoff.shape[0] - 1, doff.shape[0] - 1, q.shape[0], d.shape[0],
             q.shape[1], max(max_q_len, 1), _code(q), _stream_ptr())
     _check(rc, "maxsim_packed_backward")
+    return dq, dd
+
+
+def packed_backward_native(dscore, queries, query_offsets, documents, document_offsets,
+                           pair_query_ids, pair_document_ids, argmax, max_q_len):
+    """As ``maxsim_packed_backward`` with both gradients in the inputs' float16
+    / bfloat16 type, every row summed in fp32 and rounded once.  None when the
+    shape is not covered (short or ungrouped pair lists, fp32 inputs, dim not a
+    multiple of 8); the caller then uses the fp32 operator."""
+    if not _native_grads or queries.dtype not in (torch.float16, torch.bfloat16):
+        return None
+    dev = _require_cuda(queries, dscore, query_offsets, documents, document_offsets,
+                        pair_query_ids, pair_document_ids, argmax)
+    q, qoff, d, doff, pq, pd = _packed_args(queries, query_offsets, documents,
+                                            document_offsets, pair_query_ids, pair_document_ids)
+    g = dscore.contiguous().to(torch.float32)
+    a = argmax.contiguous().to(torch.int32)
+    n_pairs, max_q_len = pq.shape[0], int(max_q_len)
+    if g.numel() != n_pairs or tuple(a.shape) != (n_pairs, max_q_len) or n_pairs == 0:
+        return None
+    with _on_device(dev):
+        by_doc = _groups(pair_document_ids, pd, doff.shape[0] - 1)
+        by_query = _groups(pair_query_ids, pq, qoff.shape[0] - 1)
+        if by_doc is None or by_query is None:
+            return None
+        dq = torch.empty(q.shape, dtype=q.dtype, device=dev)
+        dd = torch.empty(d.shape, dtype=d.dtype, device=dev)
+        rc = load_library().maxsim_packed_backward_grouped_native(
+            _ptr(g), _ptr(q), _ptr(qoff), _ptr(d), _ptr(doff), _ptr(pq), _ptr(pd),
+            _ptr(by_query[0]), by_query[1].data_ptr(), _ptr(by_doc[0]), by_doc[1].data_ptr(), _ptr(a),
+            _ptr(dq), _ptr(dd), n_pairs, qoff.shape[0] - 1, doff.shape[0] - 1, q.shape[0], d.shape[0],
+            q.shape[1], max_q_len, _code(q), _stream_ptr())
+    if rc == _EUNSUPPORTED:
+        return None
+    _check(rc, "maxsim_packed_backward_grouped_native")
     return dq, dd
 
 

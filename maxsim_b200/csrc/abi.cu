@@ -79,8 +79,10 @@ int ensure_smem(Kernel kern, size_t smem, std::atomic<unsigned char>* done) {
 }
 
 // Mean document length up to which contrastive argmax launches tile every
-// document on its own (measured on 1024 x 1024 pairs).
-constexpr int64_t kPerDocMaxMean = 256;
+// document on its own.  Measured on 1024 x 1024 pairs, bf16, per-document tiles
+// against boundary-agnostic ones: 32-256 tokens 1.43 / 1.77 ms, 64-512 tokens
+// (mean 288) 2.43 / 2.56 ms, 300-1000 tokens 4.9-5.4 / 4.9-5.0 ms.
+constexpr int64_t kPerDocMaxMean = 320;
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -197,6 +199,17 @@ int run_forward(const PairTable& t, float* scores, int32_t* argmax, int dtype, v
 // ---------------------------------------------------------------------------
 // Backward dispatch
 // ---------------------------------------------------------------------------
+
+// grad_queries of 16-bit inputs (dim % 8 == 0, dim <= 128): one owner warp per query row.
+template <typename T, int LAYOUT>
+int launch_dq16(const PairTable& t, const float* dscore, const int32_t* argmax, void* dq,
+                int64_t q_rows, int native, cudaStream_t st) {
+  const int64_t grid = (q_rows + kBwdWarps - 1) / kBwdWarps;
+  bwd_dq_gather16_kernel<T, LAYOUT><<<(unsigned)grid, kBwdWarps * 32, 0, st>>>(t, dscore, argmax, dq,
+                                                                              q_rows, native);
+  return launch_check("bwd_dq_gather16_kernel");
+}
+
 template <typename T, int LAYOUT>
 int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argmax, float* dq,
                    float* dd, int64_t q_rows, int64_t d_rows, int64_t Nq, cudaStream_t st,
@@ -212,7 +225,7 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
       if (n_queries > 0) {
         const int64_t rows = n_queries * (int64_t)t.q_slots;
         bwd_dq_packed_kernel<T><<<(unsigned)((rows + kBwdWarps - 1) / kBwdWarps), threads, 0, st>>>(
-            t, dscore, argmax, dq, n_queries);
+            t, dscore, argmax, dq, n_queries, 0);
         if (int rc = launch_check("bwd_dq_packed_kernel")) return rc;
       }
       if (n_documents > 0) {
@@ -236,19 +249,18 @@ int run_backward_t(const PairTable& t, const float* dscore, const int32_t* argma
       return MAXSIM_OK;
     }
     if (dq) {
-      const int64_t grid = (q_rows + kBwdWarps - 1) / kBwdWarps;
       bool fast = false;
       if constexpr (sizeof(T) == 2) {
         fast = vec_ok && dim <= 128 && dim % 8 == 0 && d_rows < (1ll << 31);
         if (fast)
-          bwd_dq_gather16_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq,
-                                                                                 q_rows, 0);
+          if (int rc = launch_dq16<T, LAYOUT>(t, dscore, argmax, dq, q_rows, 0, st)) return rc;
       }
-      if (!fast)
+      if (!fast) {
+        const int64_t grid = (q_rows + kBwdWarps - 1) / kBwdWarps;
         bwd_dq_gather_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq,
                                                                              q_rows, vec_ok);
-      int rc = launch_check("bwd_dq_gather_kernel");
-      if (rc) return rc;
+        if (int rc = launch_check("bwd_dq_gather_kernel")) return rc;
+      }
     }
     if constexpr (LAYOUT == kPadded) {
       const int64_t grid = (t.n_pairs + kBwdWarps - 1) / kBwdWarps;
@@ -325,11 +337,7 @@ int run_backward_native_t(const PairTable& t, const float* dscore, const int32_t
     if (dd && ((int64_t)Nq * t.q_slots > kInvEntries || Nq > kInvMaxQ || Nb >= (1ll << 31)))
       return fail(MAXSIM_EUNSUPPORTED, "native-type gradients need Nq * Lq <= %d", kInvEntries);
   }
-  {
-    const int64_t grid = (q_rows + kBwdWarps - 1) / kBwdWarps;
-    bwd_dq_gather16_kernel<T, LAYOUT><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq, q_rows, 1);
-    if (int rc = launch_check("bwd_dq_gather16_kernel")) return rc;
-  }
+  if (int rc = launch_dq16<T, LAYOUT>(t, dscore, argmax, dq, q_rows, 1, st)) return rc;
   if constexpr (LAYOUT == kPadded) {
     const int64_t grid = (t.n_pairs + kBwdWarps - 1) / kBwdWarps;
     bwd_dd_padded_native_kernel<T><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax,
@@ -469,6 +477,12 @@ int maxsim_b200_device_status(void* stream) {
   if (cudaMemcpyFromSymbol(&v, g_device_status, sizeof(int)) != cudaSuccess) return MAXSIM_ECUDA;
   if (v != 0) cudaMemcpyToSymbol(g_device_status, &zero, sizeof(int));
   return v;
+}
+
+int maxsim_b200_wait_probe(int64_t polls, int* gave_up, void* stream) {
+  if (polls < 1 || polls > (1 << 20)) return fail(MAXSIM_EINVAL, "polls must be in [1, 2^20]");
+  tc05g::wait_probe_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>((uint32_t)polls, gave_up);
+  return launch_check("wait_probe_kernel");
 }
 
 int maxsim_b200_layout_stats(const void* offsets, int64_t n_offsets, const void* ids, int64_t n_ids,
@@ -743,6 +757,58 @@ int maxsim_packed_backward_grouped(const float* dscore, const void* queries,
   }
   return run_backward<kPacked>(t, dscore, argmax, grad_queries, grad_documents, total_q_tokens,
                                total_d_tokens, 0, dtype, stream, n_queries, n_documents);
+}
+
+int maxsim_packed_backward_grouped_native(
+    const float* dscore, const void* queries, const int32_t* query_offsets, const void* documents,
+    const int32_t* document_offsets, const int32_t* pair_query_ids,
+    const int32_t* pair_document_ids, const int32_t* order_by_query, const int32_t* ends_by_query,
+    const int32_t* order_by_document, const int32_t* ends_by_document, const int32_t* argmax,
+    void* grad_queries, void* grad_documents, int64_t n_pairs, int64_t n_queries,
+    int64_t n_documents, int64_t total_q_tokens, int64_t total_d_tokens, int64_t dim,
+    int64_t max_q_len, int dtype, void* stream) {
+  if (!fits_i32(dim) || !fits_i32(max_q_len) || !fits_i32(total_q_tokens) || !fits_i32(total_d_tokens))
+    return fail(MAXSIM_EINVAL, "packed sizes must fit int32 offsets");
+  if (n_queries < 0 || n_documents < 0 || max_q_len <= 0) return fail(MAXSIM_EINVAL, "sizes must be positive");
+  const bool ok = (dtype == MAXSIM_F16 || dtype == MAXSIM_BF16) && dim % 8 == 0 && dim <= 128 &&
+                  order_by_query && ends_by_query && order_by_document && ends_by_document &&
+                  n_pairs > 0 && n_pairs < (1ll << 31) && aligned16(queries) && aligned16(documents) &&
+                  aligned16(grad_queries) && aligned16(grad_documents) &&
+                  n_queries * max_q_len < (1ll << 33);
+  if (!ok)
+    return fail(MAXSIM_EUNSUPPORTED, "native-type packed gradients need float16 / bfloat16, grouped "
+                                     "pair lists, dim %% 8 == 0, dim <= 128 and aligned tensors");
+  if (!dscore || !argmax || !query_offsets || !document_offsets || !pair_query_ids || !pair_document_ids)
+    return fail(MAXSIM_EINVAL, "null pointer argument");
+  PairTable t = packed_table(queries, query_offsets, documents, document_offsets, pair_query_ids,
+                             pair_document_ids, n_pairs, dim, max_q_len, total_q_tokens,
+                             total_d_tokens);
+  t.order_q = order_by_query; t.ends_q = ends_by_query;
+  t.order_d = order_by_document; t.ends_d = ends_by_document;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned threads = kBwdWarps * 32;
+  if (n_queries > 0) {
+    const int64_t rows = n_queries * max_q_len;
+    if (dtype == MAXSIM_F16)
+      bwd_dq_packed_kernel<__half><<<(unsigned)((rows + kBwdWarps - 1) / kBwdWarps), threads, 0, st>>>(
+          t, dscore, argmax, grad_queries, n_queries, 1);
+    else
+      bwd_dq_packed_kernel<__nv_bfloat16><<<(unsigned)((rows + kBwdWarps - 1) / kBwdWarps), threads, 0, st>>>(
+          t, dscore, argmax, grad_queries, n_queries, 1);
+    if (int rc = launch_check("bwd_dq_packed_kernel")) return rc;
+  }
+  if (n_documents > 0) {
+    const size_t smem = (size_t)kBwdWarps * sizeof(PdnWarp);
+    const unsigned grid = (unsigned)((n_documents + kBwdWarps - 1) / kBwdWarps);
+    if (dtype == MAXSIM_F16)
+      bwd_dd_packed_native_kernel<__half><<<grid, threads, smem, st>>>(
+          t, dscore, argmax, reinterpret_cast<__half*>(grad_documents), n_documents);
+    else
+      bwd_dd_packed_native_kernel<__nv_bfloat16><<<grid, threads, smem, st>>>(
+          t, dscore, argmax, reinterpret_cast<__nv_bfloat16*>(grad_documents), n_documents);
+    if (int rc = launch_check("bwd_dd_packed_native_kernel")) return rc;
+  }
+  return MAXSIM_OK;
 }
 
 int maxsim_packed_backward(const float* dscore, const void* queries, const int32_t* query_offsets,

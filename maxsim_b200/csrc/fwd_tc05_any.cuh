@@ -696,6 +696,20 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
 }
 
+// One thread waits `limit` polls for a barrier phase that nothing will ever
+// complete, with the same bounded wait the kernels above use: it has to give
+// up, record the status bit and return.  Nothing asynchronous is in flight, so
+// the wait running out cannot leave anything behind; the next launch finds a
+// clean device.  For the test of the time-out reporting path.
+__global__ void wait_probe_kernel(uint32_t limit, int* gave_up) {
+  __shared__ __align__(8) unsigned long long bar;
+  const uint32_t b = smem_u32(&bar);
+  mbar_init(b, 1);
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  const bool done = wait_bounded(b, 0u, limit);
+  if (gave_up) *gave_up = done ? 0 : 1;
+}
+
 }  // namespace tc05g
 
 // ---------------------------------------------------------------------------

@@ -118,6 +118,23 @@ def score_candidates_padded_sharded(queries, documents, query_lengths, doc_lengt
 # Contrastive training: all-gather documents, per-owner gradient reduction
 # ---------------------------------------------------------------------------
 
+_INT_TABLES = {}
+
+
+def _device_ints(values: Sequence[int], device) -> torch.Tensor:
+    """A small int32 table on ``device``.  Tables are kept: a training loop asks
+    for the same shard boundaries every step, and a host-to-device copy from
+    pageable memory makes the host wait for the stream."""
+    key = (str(device), tuple(values))
+    table = _INT_TABLES.get(key)
+    if table is None:
+        if len(_INT_TABLES) > 64:
+            _INT_TABLES.clear()
+        table = torch.tensor(list(values), dtype=torch.int32, device=device)
+        _INT_TABLES[key] = table
+    return table
+
+
 class _Done:
     """Stands in for the handle of an exchange that has already completed."""
 
@@ -272,8 +289,7 @@ class _ShardedContrastive(torch.autograd.Function):
         nq_local, lq = q.shape[0], q.shape[1]
         pack = getattr(ops, "pack_owner_records", None)
         if pack is not None and g.is_cuda:
-            col_start = torch.tensor(col0, dtype=torch.int32).to(g.device, non_blocking=True)
-            send = pack(argmax, g, col_start)
+            send = pack(argmax, g, _device_ints(col0, g.device))
         else:
             record = torch.cat([argmax.to(torch.int32), g.view(torch.int32).unsqueeze(-1)], dim=2)
             send = torch.cat([record[:, col0[o]:col0[o + 1]].reshape(-1) for o in range(world)])

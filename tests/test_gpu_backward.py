@@ -165,6 +165,51 @@ def test_autocast_compile_and_stability():
     assert torch.isfinite(q.grad).all()
 
 
+def test_autocast_and_compile_on_the_padded_and_packed_train_paths():
+    """The differentiable padded and packed operators under torch.autocast and
+    torch.compile(fullgraph=False) (reference: tests/test_compat.py:36-152)."""
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(4)
+    q = torch.randn(3, 16, 64, generator=g).to(DEV, dt).requires_grad_(True)
+    d = torch.randn(3, 5, 40, 64, generator=g).to(DEV, dt).requires_grad_(True)
+    qlen = torch.tensor([16, 9, 12], dtype=torch.int32, device=DEV)
+    dlen = torch.randint(1, 41, (3, 5), generator=g, dtype=torch.int32).to(DEV)
+
+    def padded_step(q, d):
+        return maxsim.score_candidates_padded_train(q, d, qlen, dlen).sum()
+
+    with torch.autocast(device_type="cuda", dtype=dt):
+        loss = padded_step(q, d)
+    loss.backward()
+    assert torch.isfinite(loss) and torch.isfinite(q.grad).all() and torch.isfinite(d.grad).all()
+    eager = padded_step(q.detach(), d.detach())
+    out = torch.compile(padded_step, fullgraph=False)(q.detach(), d.detach())
+    torch.testing.assert_close(out, eager, rtol=1e-3, atol=1e-3)
+
+    qp = torch.randn(30, 64, generator=g).to(DEV, dt).requires_grad_(True)
+    dp = torch.randn(90, 64, generator=g).to(DEV, dt).requires_grad_(True)
+    qoff = torch.tensor([0, 7, 19, 30], dtype=torch.int32, device=DEV)
+    doff = torch.tensor([0, 25, 26, 60, 90], dtype=torch.int32, device=DEV)
+    pq = torch.tensor([0, 2, 1, 1, 0], dtype=torch.int32, device=DEV)
+    pd = torch.tensor([3, 0, 1, 3, 3], dtype=torch.int32, device=DEV)
+
+    def packed_step(q, d):
+        return maxsim.score_pairs_packed_train(q, qoff, d, doff, pq, pd).sum()
+
+    with torch.autocast(device_type="cuda", dtype=dt):
+        loss = packed_step(qp, dp)
+    loss.backward()
+    assert torch.isfinite(loss) and torch.isfinite(qp.grad).all() and torch.isfinite(dp.grad).all()
+    eager = packed_step(qp.detach(), dp.detach())
+    out = torch.compile(packed_step, fullgraph=False)(qp.detach(), dp.detach())
+    torch.testing.assert_close(out, eager, rtol=1e-3, atol=1e-3)
+    # gradients through the compiled functions equal the eager ones
+    q2 = q.detach().clone().requires_grad_(True)
+    d2 = d.detach().clone().requires_grad_(True)
+    torch.compile(padded_step, fullgraph=False)(q2, d2).backward()
+    assert torch.equal(q2.grad, q.grad) and torch.equal(d2.grad, d.grad)
+
+
 def test_training_reduces_contrastive_loss():
     """In-batch InfoNCE on the contrastive op converges (reference:
     tests/test_train_convergence.py:90-112)."""
@@ -224,3 +269,32 @@ def test_fused_contrastive_loss_matches_cross_entropy(temperature, dtype):
         maxsim.contrastive_loss(q1, d1, off, temperature=0.0)
     with pytest.raises(ValueError, match="targets"):
         maxsim.contrastive_loss(q1, d1, off, targets[:3])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_grad_queries_alone_with_argmax_entries_outside_their_document(dtype):
+    """grad_queries without grad_documents (what a rank of the sharded step
+    computes), fp32 and in the leaf dtype, with many query rows, documents of
+    very different lengths and argmax entries outside their document, which
+    route nowhere."""
+    g = torch.Generator().manual_seed(7)
+    Nq, Lq, dim = 1250, 32, 128
+    lens = [5, 1, 800, 300, 129, 1700, 64, 2, 33]
+    q = torch.randn(Nq, Lq, dim, generator=g).to(DEV, dtype)
+    d = torch.randn(sum(lens), dim, generator=g).to(DEV, dtype)
+    off = torch.zeros(len(lens) + 1, dtype=torch.int32)
+    off[1:] = torch.tensor(lens).cumsum(0)
+    off = off.to(DEV)
+    w = torch.randn(Nq, len(lens), generator=g).to(DEV)
+    a = torch.stack([torch.randint(0, n, (Nq, Lq), generator=g) for n in lens], dim=1).to(DEV, torch.int32)
+    a[3, 2, 5] = 10 ** 6
+    a[7, 0, 1] = -4
+    dq, none = _ops.contrastive_backward_part(w, q, d, off, a, want_queries=True, want_documents=False)
+    assert none is None
+    native = _ops.contrastive_backward_native(w, q, d, off, a, want_documents=False)
+    assert native is not None and native[1] is None
+    assert torch.equal(native[0], dq.to(dtype))
+    sel = [0, 3, 7, 640, 1249]
+    wq, _ = oracle.contrastive_backward(f32(w[sel]), f32(q[sel]), f32(d), i64(off), a.cpu().numpy()[sel])
+    assert_grads(f32(dq[sel]), wq, NAME_OF[dtype])
+    assert _ops.device_status() == 0

@@ -211,23 +211,42 @@ def test_packed_int64_indices_and_empty_pairs():
     assert s.shape == (0,) and am.shape == (0, 9)
 
 
+# Random shapes, 50 per layout and dtype, with the shape distributions of the
+# reference's fuzz suite (tests/test_fuzz.py:51-170 there); the contrastive one also
+# draws query counts large enough for the tensor-core kernels.
+FUZZ_ITERS = 50
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
-def test_fuzz_all_layouts(dtype):
+def test_fuzz_padded(dtype):
     rng = random.Random(123)
-    for it in range(25):
+    for it in range(FUZZ_ITERS):
         dim = rng.choice([16, 24, 32, 64, 96, 128])
         B, C = rng.randint(1, 4), rng.randint(1, 8)
         Lq, Ld = rng.randint(1, 64), rng.randint(1, 200)
         q, d, qlen, dlen = _rand_padded(B, C, Lq, Ld, dim, dtype, 1000 + it)
         _check_padded(q, d, qlen, dlen, dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fuzz_packed(dtype):
+    rng = random.Random(7777)
+    for it in range(FUZZ_ITERS):
+        dim = rng.choice([16, 24, 32, 64, 96, 128])
         q_lens = [rng.randint(1, 32) for _ in range(rng.randint(1, 6))]
         d_lens = [rng.randint(1, 128) for _ in range(rng.randint(1, 8))]
         args = _rand_packed(q_lens, d_lens, rng.randint(1, 16), dim, dtype, 2000 + it)
         _check_packed(*args, dtype)
-        Lqc = rng.choice([16, 32, 48, 64])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_fuzz_contrastive(dtype):
+    rng = random.Random(31337)
+    for it in range(FUZZ_ITERS):
+        Lq = rng.choice([16, 32, 48, 64])
         dl = [rng.randint(1, 200) for _ in range(rng.randint(1, 8))]
-        qc, dc, off = _rand_contrastive(rng.randint(1, 6), Lqc, dl, rng.choice([16, 32, 64, 96, 128]),
-                                        dtype, 3000 + it)
+        nq = rng.randint(1, 6) if it % 2 else rng.randint(8, 40)
+        qc, dc, off = _rand_contrastive(nq, Lq, dl, rng.choice([16, 32, 64, 96, 128]), dtype, 3000 + it)
         _check_contrastive(qc, dc, off, dtype)
 
 

@@ -123,3 +123,46 @@ def test_autograd_results_do_not_depend_on_the_switch(api):
         assert torch.equal(grads[0][1], grads[1][1])
     else:  # summation order of grad_documents varies between launches (see above)
         torch.testing.assert_close(grads[0][1].float(), grads[1][1].float(), rtol=2.0 ** -6, atol=1e-4)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("n_pairs,n_docs,n_queries,dim", [(4096, 300, 80, 96), (3000, 7, 40, 128),
+                                                         (2048, 2000, 3, 64), (20000, 11, 11, 32)])
+def test_packed_native_gradients_match_the_fp32_operator(n_pairs, n_docs, n_queries, dim, dtype):
+    """Grouped pair lists: both gradients in the leaf dtype, every row summed in
+    fp32 and stored once.  grad_queries is the fp32 operator's result rounded
+    once (same kernel, same order); grad_documents sums in pair-list order
+    instead of the operator's read-modify-write order, so it may differ in the
+    last place; few documents with many pairs (7 or 11 documents for thousands
+    of pairs) exercise the batches of 512 terms, and both launches of the same
+    call must give the same bits."""
+    from maxsim_b200 import workloads as W
+    from _util import assert_grads, f32, oracle
+    name = "fp16" if dtype == torch.float16 else "bf16"
+    wl = W.c4_packed_grid_fp16(seed=n_pairs % 97, n_queries=n_queries, n_docs=n_docs,
+                               n_pairs=n_pairs, dim=dim)
+    q = W.to_torch(wl.queries, name, DEV)
+    d = W.to_torch(wl.documents, name, DEV)
+    qo = torch.from_numpy(wl.query_offsets).to(DEV)
+    do = torch.from_numpy(wl.document_offsets).to(DEV)
+    pq = torch.from_numpy(wl.pair_query_ids).to(DEV)
+    pd = torch.from_numpy(wl.pair_document_ids).to(DEV)
+    w = torch.from_numpy(wl.dscore).to(DEV)
+    _, a = maxsim.score_pairs_packed_with_argmax(q, qo, d, do, pq, pd, max_q_len=32)
+    native = _ops.packed_backward_native(w, q, qo, d, do, pq, pd, a, 32)
+    assert native is not None and native[0].dtype == dtype and native[1].dtype == dtype
+    again = _ops.packed_backward_native(w, q, qo, d, do, pq, pd, a, 32)
+    assert torch.equal(native[0], again[0]) and torch.equal(native[1], again[1])
+    dq32, dd32 = _ops.ops.maxsim_packed_backward(w, q, qo, d, do, pq, pd, a, 32)
+    assert torch.equal(native[0], dq32.to(dtype))
+    wq, wd = oracle.pairs_packed_backward(wl.dscore, f32(q), wl.query_offsets, f32(d), wl.document_offsets,
+                                          wl.pair_query_ids, wl.pair_document_ids, a.cpu().numpy())
+    assert_grads(f32(native[1]), wd, name)
+    assert_grads(f32(native[0]), wq, name)
+    # through autograd: the leaves receive the native tensors
+    qr, dr = q.clone().requires_grad_(True), d.clone().requires_grad_(True)
+    maxsim.score_pairs_packed_train(qr, qo, dr, do, pq, pd, max_q_len=32).backward(w)
+    assert torch.equal(qr.grad, native[0]) and torch.equal(dr.grad, native[1])
+    # short lists are not grouped: the fp32 operator serves them
+    assert _ops.packed_backward_native(w[:100], q, qo, d, do, pq[:100].contiguous(), pd[:100].contiguous(),
+                                       a[:100].contiguous(), 32) is None

@@ -92,3 +92,22 @@ def test_a_tensor_is_inspected_again_after_it_is_written():
     fresh = torch.tensor([0, 32, 64, 96, 127], dtype=torch.int32, device=DEV)  # a new object is never trusted
     with pytest.raises(ValueError, match="total doc tokens"):
         maxsim.score_contrastive(q, docs, fresh)
+
+
+def test_a_wait_that_runs_out_is_reported_and_leaves_the_device_clean():
+    """The kernels' waits are bounded: one that runs out sets a status bit the
+    host can read.  The probe kernel waits on a barrier nothing arrives at (no
+    copy or MMA is in flight, so giving up leaves nothing behind); the status
+    word has to show the time-out once, and the operators have to work after."""
+    import maxsim_b200 as maxsim
+    from maxsim_b200 import _ops
+    assert _ops.device_status() == 0
+    assert _ops.wait_probe(polls=32) is True
+    assert _ops.device_status() == 2          # the bounded-wait bit of the tensor-core kernels
+    assert _ops.device_status() == 0          # reading clears it
+    g = torch.Generator().manual_seed(0)
+    q = torch.randn(16, 32, 128, generator=g).to("cuda", torch.bfloat16)
+    d = torch.randn(400, 128, generator=g).to("cuda", torch.bfloat16)
+    off = torch.tensor([0, 100, 250, 400], dtype=torch.int32, device="cuda")
+    s, a = maxsim.score_contrastive_with_argmax(q, d, off)
+    assert torch.isfinite(s).all() and _ops.device_status() == 0
