@@ -641,10 +641,14 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
         a0, a1 = mdist.shard_range(n, r, world)
         shard_sizes.append((int(lens_host[a0:a1].sum()), a1 - a0, a1 - a0))
 
+    # the record exchange of the backward pass on a group with NCCL's default CTA count
+    records_group = dist.new_group(backend="nccl")
+
     def one_step(exchange, sizes, keep=False):
         q.grad = None
         d.grad = None
-        s = mdist.score_contrastive_sharded(q, d, lens, exchange=exchange, shard_sizes=sizes)
+        s = mdist.score_contrastive_sharded(q, d, lens, exchange=exchange, shard_sizes=sizes,
+                                            records_group=records_group)
         if keep:
             s.retain_grad()
         # every rank averages over its own queries; the global mean is over all n
@@ -775,8 +779,10 @@ def run_contrastive_profile(args):
     torch.cuda.set_device(dev)
     n = 512 if args.small else 1024
     # --short-docs: 32-256 tokens per document, the range served by the kernel
-    # whose tiles start at document starts
-    data = W.c5_device(dev, Nq=n, Nb=n, lo=32, hi=256) if args.short_docs else W.c5_device(dev, Nq=n, Nb=n)
+    # whose tiles start at document starts; --lq / --dim: another query length or
+    # dim (the general tcgen05 kernel instead of the Lq = 32, dim = 128 one)
+    lo, hi = (32, 256) if args.short_docs else (64, 512)
+    data = W.c5_device(dev, Nq=n, Nb=n, lo=lo, hi=hi, Lq=args.lq, dim=args.dim)
     q = data["queries"].requires_grad_(True)
     d = data["documents"].requires_grad_(True)
     off = data["document_offsets"]
@@ -785,7 +791,8 @@ def run_contrastive_profile(args):
         contrastive_train_step(maxsim, q, d, off, target)
     ms = _event_ms(lambda: contrastive_train_step(maxsim, q, d, off, target), max(1, args.steps))
     print(json.dumps({"profile_run": True, "workload": "c5_contrastive_ties_bf16", "Nq": n, "Nb": n,
-                      "doc_tokens": int(d.shape[0]), "ms_per_step": statistics.median(ms)}), flush=True)
+                      "Lq": args.lq, "dim": args.dim, "doc_tokens": int(d.shape[0]),
+                      "ms_per_step": statistics.median(ms)}), flush=True)
 
 
 def run_packed_profile(args):
@@ -835,7 +842,13 @@ def run_gpu_arm(args):
     if world > 1:
         import torch.distributed as dist_mod
         dist = dist_mod
-        dist.init_process_group("nccl", device_id=dev)
+        # Collectives run beside persistent compute kernels that leave them a few SMs: keep
+        # NCCL's kernels within those, on a high-priority stream
+        from maxsim_b200 import dist as mdist
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        opts.config.max_ctas = mdist.COLLECTIVE_SMS
+        opts.config.cga_cluster_size = 1  # single CTAs fit the scattered free SMs; clusters do not
+        dist.init_process_group("nccl", device_id=dev, pg_options=opts)
     peaks = _peaks()
 
     Nq, Lq, C, Ld, dim = (C3[k] for k in ("Nq", "Lq", "C", "Ld", "dim"))
@@ -1098,6 +1111,8 @@ def main():
                          "(Nq=Nb=1024, or 512 with --small); for profiler captures")
     ap.add_argument("--short-docs", action="store_true",
                     help="with --profile-contrastive: documents of 32-256 tokens instead of 64-512")
+    ap.add_argument("--lq", type=int, default=32, help="with --profile-contrastive: query length")
+    ap.add_argument("--dim", type=int, default=128, help="with --profile-contrastive: embedding dim")
     ap.add_argument("--profile-packed", action="store_true",
                     help="run only train steps of the packed pair grid (65536 pairs); for profiler captures")
     ap.add_argument("--list-order", action="store_true",

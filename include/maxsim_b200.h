@@ -325,14 +325,17 @@ MAXSIM_API int maxsim_contrastive_forward_with_argmax(
  * q * out_ld + out_col0 + d of scores [Nq, out_ld] / argmax [Nq, out_ld, Lq]:
  * launches over different document ranges, or different document tensors,
  * fill one matrix.  block_tokens: tokens in the block if known, else 0 (steers
- * the choice of tiling only).  MAXSIM_EUNSUPPORTED, with nothing written, for
+ * the choice of tiling only).  reserve_sms: SMs the persistent kernel leaves
+ * unused, for the kernels of a collective that is meant to run beside this
+ * launch (0 = use all).  MAXSIM_EUNSUPPORTED, with nothing written, for
  * shapes outside the tcgen05 kernel (float16 / bfloat16, Lq <= 64, dim a
  * multiple of 16 up to 128, at least 2 * 128 / lanes-per-query queries). */
 MAXSIM_API int maxsim_contrastive_forward_with_argmax_block(
     const void* queries, const void* documents, const int32_t* document_offsets,
     float* scores, int32_t* argmax,
     int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim, int64_t total_d_tokens,
-    int64_t block_tokens, int64_t out_ld, int64_t out_col0, int dtype, void* stream);
+    int64_t block_tokens, int64_t out_ld, int64_t out_col0, int64_t reserve_sms,
+    int dtype, void* stream);
 
 /* Sharded training, owner exchange (no reference counterpart).
  * pack_owner_records regroups the pairs of a rank's queries by the rank that

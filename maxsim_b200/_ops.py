@@ -63,7 +63,7 @@ _SIGNATURES = {
     "maxsim_contrastive_forward": (c_int, [_P] * 4 + [_I64] * 5 + [c_int, _P]),
     "maxsim_contrastive_forward_with_argmax": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, _P]),
     "maxsim_contrastive_backward": (c_int, [_P] * 7 + [_I64] * 5 + [c_int, _P]),
-    "maxsim_contrastive_forward_with_argmax_block": (c_int, [_P] * 5 + [_I64] * 8 + [c_int, _P]),
+    "maxsim_contrastive_forward_with_argmax_block": (c_int, [_P] * 5 + [_I64] * 9 + [c_int, _P]),
     "maxsim_b200_pack_owner_records": (c_int, [_P] * 3 + [_I64] * 4 + [_P, _P]),
     "maxsim_contrastive_backward_documents_from_records": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, c_int, _P]),
     "maxsim_padded_backward_native": (c_int, [_P] * 8 + [_I64] * 5 + [c_int, _P]),
@@ -755,14 +755,16 @@ def maxsim_contrastive_forward_with_argmax(queries, documents, document_offsets)
 
 
 def contrastive_forward_block(queries, documents, block_offsets, scores, argmax, col0: int,
-                              block_tokens: int = 0) -> bool:
+                              block_tokens: int = 0, reserve_sms: int = 0) -> bool:
     """Scores ``queries [Nq, Lq, D]`` against the documents described by
     ``block_offsets [n + 1]`` (absolute token rows of the packed ``documents``)
     and writes them into columns ``[col0, col0 + n)`` of the caller's
     ``scores [Nq, Nb_total]`` fp32 and ``argmax [Nq, Nb_total, Lq]`` int32: several
     launches over different document ranges (or different ``documents``
     tensors) fill one score matrix.  ``block_tokens`` is the number of tokens
-    in the block when known (it steers the choice of tiling).  Returns False
+    in the block when known (it steers the choice of tiling); ``reserve_sms``
+    SMs are left unused for a collective meant to run beside the launch (the
+    kernel otherwise holds every SM until it ends).  Returns False
     when the shape is outside what the tcgen05 kernel covers (nothing was
     written); the caller then scores the block on its own and copies."""
     dev = _require_cuda(queries, documents, block_offsets, scores, argmax)
@@ -776,8 +778,8 @@ def contrastive_forward_block(queries, documents, block_offsets, scores, argmax,
     with _on_device(dev):
         rc = load_library().maxsim_contrastive_forward_with_argmax_block(
             _ptr(q), _ptr(d), _ptr(off), scores.data_ptr(), argmax.data_ptr(),
-            Nq, Lq, n, dim, d.shape[0], int(block_tokens), scores.shape[1], int(col0), _code(q),
-            _stream_ptr())
+            Nq, Lq, n, dim, d.shape[0], int(block_tokens), scores.shape[1], int(col0),
+            int(reserve_sms), _code(q), _stream_ptr())
     if rc == _EUNSUPPORTED:
         return False
     _check(rc, "maxsim_contrastive_forward_with_argmax_block")

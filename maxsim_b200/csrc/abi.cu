@@ -170,11 +170,15 @@ int run_forward(const PairTable& t, float* scores, int32_t* argmax, int dtype, v
     const bool per_document =
         ARGMAX && (path == 8 || (path != 9 && t.block_rows <= kPerDocMaxMean * (int64_t)t.C));
     int rc;
+    // the persistent kernels take one CTA per SM; a launch that runs beside a collective
+    // leaves t.reserve_sms of them to the collective's kernels
+    int sms = sm_count() - t.reserve_sms;
+    if (sms < 8) sms = 8;
     if (tc05_eligible(t, dtype))  // Lq = 32, dim = 128
-      rc = per_document ? launch_tc05_doc<ARGMAX>(t, scores, argmax, dtype, sm_count(), st)
-                        : launch_tc05<ARGMAX>(t, scores, argmax, dtype, sm_count(), st);
+      rc = per_document ? launch_tc05_doc<ARGMAX>(t, scores, argmax, dtype, sms, st)
+                        : launch_tc05<ARGMAX>(t, scores, argmax, dtype, sms, st);
     else
-      rc = launch_tc05g<ARGMAX>(t, scores, argmax, dtype, sm_count(), st, per_document);
+      rc = launch_tc05g<ARGMAX>(t, scores, argmax, dtype, sms, st, per_document);
     if (rc == 0) return launch_check("fwd_tc05_kernel");
     if (rc < 0) return fail(MAXSIM_ECUDA, "could not configure the tcgen05 kernel");
     // rc == 1: tensor maps could not be encoded; use the streaming kernel
@@ -422,7 +426,7 @@ PairTable contrastive_table(const void* q, const void* d, const int32_t* doff, i
   t.n_pairs = Nq * Nb; t.dim = (int32_t)dim; t.q_slots = (int32_t)Lq;
   t.q_rows = Nq * Lq; t.d_rows = d_rows;
   t.Ld_max = 0; t.C = (int32_t)(Nb > 0 ? Nb : 1);
-  t.out_ld = t.C; t.out_col0 = 0; t.block_rows = d_rows;
+  t.out_ld = t.C; t.out_col0 = 0; t.block_rows = d_rows; t.reserve_sms = 0;
   return t;
 }
 
@@ -901,7 +905,8 @@ int maxsim_contrastive_forward_with_argmax(const void* queries, const void* docu
 int maxsim_contrastive_forward_with_argmax_block(
     const void* queries, const void* documents, const int32_t* document_offsets, float* scores,
     int32_t* argmax, int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim, int64_t total_d_tokens,
-    int64_t block_tokens, int64_t out_ld, int64_t out_col0, int dtype, void* stream) {
+    int64_t block_tokens, int64_t out_ld, int64_t out_col0, int64_t reserve_sms, int dtype,
+    void* stream) {
   if (Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(dim) || !fits_i32(Lq) || !fits_i32(Nb) ||
       !fits_i32(total_d_tokens))
     return fail(MAXSIM_EINVAL, "Lq and dim must be > 0 and sizes must fit int32");
@@ -913,6 +918,7 @@ int maxsim_contrastive_forward_with_argmax_block(
   t.out_ld = out_ld;
   t.out_col0 = out_col0;
   t.block_rows = block_tokens > 0 ? block_tokens : total_d_tokens;
+  t.reserve_sms = reserve_sms > 0 ? (int32_t)(reserve_sms < 1024 ? reserve_sms : 1024) : 0;
   return run_forward<kContrastive, true>(t, scores, argmax, dtype, stream);
 }
 
@@ -924,11 +930,14 @@ int maxsim_b200_pack_owner_records(const int32_t* argmax, const float* dscore,
     return fail(MAXSIM_EINVAL, "sizes must be >= 0 (Lq, n_owners > 0) and fit int32");
   if (Nq * Nb == 0) return MAXSIM_OK;
   if (!argmax || !dscore || !col_start || !send) return fail(MAXSIM_EINVAL, "null pointer argument");
-  const int64_t pairs = Nq * Nb;
-  const int64_t grid = (pairs + 7) / 8;
-  if (grid >= (1ll << 31)) return fail(MAXSIM_EINVAL, "too many pairs");
-  pack_owner_records_kernel<<<(unsigned)grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      argmax, dscore, col_start, (int)n_owners, (int)Nq, (int)Nb, (int)Lq, send);
+  if (n_owners > 65535) return fail(MAXSIM_EINVAL, "too many owners");
+  // about one wave of CTAs over all owners, each thread copying several words
+  int64_t gx = ((int64_t)sm_count() * 8 + n_owners - 1) / n_owners;
+  const int64_t need = (Nq * Nb * (Lq + 1) / n_owners + 255) / 256;
+  if (gx > need) gx = need > 0 ? need : 1;
+  dim3 grid((unsigned)gx, (unsigned)n_owners);
+  pack_owner_records_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      argmax, dscore, col_start, (int)Nq, (int)Nb, (int)Lq, send);
   return launch_check("pack_owner_records_kernel");
 }
 

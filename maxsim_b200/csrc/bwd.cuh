@@ -241,7 +241,10 @@ bwd_dq_gather16_kernel(PairTable t, const float* __restrict__ dscore,
         }
       }
       const int n = min(32, C - c0);
-      if (n == 32 && k_ok && __all_sync(0xffffffffu, src >= 0)) {
+      // (the vote is taken by all lanes before anything lane-dependent is tested: lanes past
+      // the row's last element, dim < 128, must not skip it)
+      const bool all_routed = __all_sync(0xffffffffu, src >= 0);
+      if (n == 32 && all_routed) {
         // all 32 candidates routed (the usual case): no per-row checks
 #pragma unroll 1
         for (int l0 = 0; l0 < 32; l0 += 8) {
@@ -252,7 +255,8 @@ bwd_dq_gather16_kernel(PairTable t, const float* __restrict__ dscore,
             const int l = l0 + 2 * u + half;
             gw[u] = __shfl_sync(0xffffffffu, gl, l);
             const int32_t sr = __shfl_sync(0xffffffffu, src, l);
-            rows[u].load(D + (int64_t)sr * dim + k);
+            rows[u].zero();
+            if (k_ok) rows[u].load(D + (int64_t)sr * dim + k);
           }
 #pragma unroll
           for (int u = 0; u < 4; ++u) rows[u].fma_into(gw[u], acc);
@@ -1018,25 +1022,27 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
 // bits of its score gradient.  Blocks of all ranks' queries, concatenated in
 // rank order by the all-to-all, are the [all queries][own documents][Lq + 1]
 // tensor that bwd_dd_invert_kernel reads with rec_stride = Lq + 1.
-// One warp per pair.
+// One thread per word of `send`; blockIdx.y is the owner, so that its column
+// range is uniform over the block and both sides of the copy are coalesced.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 pack_owner_records_kernel(const int32_t* __restrict__ argmax, const float* __restrict__ dscore,
-                          const int32_t* __restrict__ col_start, int n_owners, int Nq, int Nb, int Lq,
+                          const int32_t* __restrict__ col_start, int Nq, int Nb, int Lq,
                           int32_t* __restrict__ send) {
-  const int lane = threadIdx.x & 31;
-  const int64_t pair = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (pair >= (int64_t)Nq * Nb) return;
-  const int q = (int)(pair / Nb), c = (int)(pair - (int64_t)q * Nb);
-  // owner of column c: the last o with col_start[o] <= c (few owners: a scan)
-  int o = 0;
-  while (o + 1 < n_owners && __ldg(col_start + o + 1) <= c) ++o;
+  const int o = blockIdx.y;
   const int c0 = __ldg(col_start + o), n_o = __ldg(col_start + o + 1) - c0;
   const int rec = Lq + 1;
-  int32_t* dst = send + ((int64_t)c0 * Nq + (int64_t)q * n_o + (c - c0)) * rec;
-  const int32_t* src = argmax + pair * Lq;
-  for (int i = lane; i < Lq; i += 32) dst[i] = __ldg(src + i);
-  if (lane == 0) dst[Lq] = __float_as_int(__ldg(dscore + pair));
+  const int64_t words = (int64_t)Nq * n_o * rec;          // of this owner's block
+  int32_t* dst = send + (int64_t)c0 * Nq * rec;
+  const int64_t per_query = (int64_t)n_o * rec;
+  for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < words;
+       w += (int64_t)gridDim.x * blockDim.x) {
+    const int q = (int)(w / per_query);
+    const int r = (int)(w - (int64_t)q * per_query);
+    const int dl = r / rec, slot = r - dl * rec;
+    const int64_t pair = (int64_t)q * Nb + c0 + dl;
+    dst[w] = slot < Lq ? __ldg(argmax + pair * Lq + slot) : __float_as_int(__ldg(dscore + pair));
+  }
 }
 
 }  // namespace maxsim

@@ -53,6 +53,7 @@ struct PairTable {
   int64_t out_ld;
   int64_t out_col0;
   int64_t block_rows;  // document rows this launch covers (d_rows unless a block of a larger tensor)
+  int32_t reserve_sms; // SMs the persistent forward leaves free (for a collective running beside it)
 };
 
 struct PairGeom {

@@ -251,31 +251,22 @@ __device__ __forceinline__ void commit_segment(float km, const uint32_t* v, int 
   }
 }
 
-// The MMAs of one document tile against both accumulators, K = 16 * KS.  The
-// issuing thread's instruction stream sets the pace of the tensor pipe, so the
-// common case (dim 128) is unrolled at compile time.
-template <int KS>
+// The MMAs of one document tile against both accumulators, K = 16 * ksteps.
+// Inlined into the issuing thread's code on purpose: that thread runs with the
+// 40 registers setmaxnreg left it, a budget the compiler keeps only for code
+// it compiles as part of the kernel -- an out-of-line callee would be compiled
+// to its own, larger, register count.
 __device__ __forceinline__ void issue_mmas(uint32_t d_tmem, uint32_t smA, uint32_t b_tile,
-                                           uint32_t idesc) {
+                                           uint32_t idesc, int ksteps) {
 #pragma unroll
   for (int sub = 0; sub < kMSub; ++sub) {
 #pragma unroll
-    for (int k = 0; k < KS; ++k) {
-      const uint64_t ad = umma_desc(smA + sub * kATileBytes + (k >> 2) * kBoxBytes + (k & 3) * 32);
-      const uint64_t bd = umma_desc(b_tile + (k >> 2) * kBoxBytes + (k & 3) * 32);
-      umma_f16(d_tmem + sub * kBN, ad, bd, idesc, k > 0 ? 1u : 0u);
-    }
-  }
-}
-// Any other dim (a multiple of 16 below 128): a run-time K loop, out of line so
-// that it does not weigh on the registers of the widest case.
-__device__ __noinline__ void issue_mmas_any(uint32_t d_tmem, uint32_t smA, uint32_t b_tile,
-                                            uint32_t idesc, int ksteps) {
-  for (int sub = 0; sub < kMSub; ++sub) {
-    for (int k = 0; k < ksteps; ++k) {
-      const uint64_t ad = umma_desc(smA + sub * kATileBytes + (k >> 2) * kBoxBytes + (k & 3) * 32);
-      const uint64_t bd = umma_desc(b_tile + (k >> 2) * kBoxBytes + (k & 3) * 32);
-      umma_f16(d_tmem + sub * kBN, ad, bd, idesc, k > 0 ? 1u : 0u);
+    for (int k = 0; k < kMaxDim / 16; ++k) {
+      if (k < ksteps) {
+        const uint64_t ad = umma_desc(smA + sub * kATileBytes + (k >> 2) * kBoxBytes + (k & 3) * 32);
+        const uint64_t bd = umma_desc(b_tile + (k >> 2) * kBoxBytes + (k & 3) * 32);
+        umma_f16(d_tmem + sub * kBN, ad, bd, idesc, k > 0 ? 1u : 0u);
+      }
     }
   }
 }
@@ -451,10 +442,7 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           const uint32_t b_tile = smB + bs * kBTileBytes;
           const uint32_t d_tmem = tmem_base + acc * (kMSub * kBN);
-          // this thread's instruction stream sets the pace of the tensor pipe: the K loop of
-          // the widest case is unrolled at compile time
-          if (P.ksteps == kMaxDim / 16) issue_mmas<kMaxDim / 16>(d_tmem, smA, b_tile, idesc);
-          else issue_mmas_any(d_tmem, smA, b_tile, idesc, P.ksteps);
+          issue_mmas(d_tmem, smA, b_tile, idesc, P.ksteps);
           umma_commit(b_empty + 8 * bs);  // slot reusable once these MMAs retire
           umma_commit(t_full + 8 * acc);  // accumulators ready for the epilogue
           if (++bs == kBStages) { bs = 0; bph ^= 1u; }

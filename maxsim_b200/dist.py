@@ -12,13 +12,14 @@ Rerank (padded / packed candidates)
 Contrastive training
     Rank r owns ``Nq/R`` queries and ``Nb/R`` documents.
 
-    Forward: the packed document shards (ragged) are all-gathered straight
-    into one packed buffer ``[T_total, D]`` in rank order -- no padding rows,
-    no compaction -- together with their lengths.  While that exchange runs,
-    the rank's queries are already scored against its OWN documents; the
-    remaining column blocks follow when the buffer is complete.  All launches
-    write into one ``[Nq_local, Nb_total]`` score matrix (document columns in
-    rank order, so diagonal targets are ``rank_query_offset + arange``).
+    Forward: the packed document shards (ragged) are gathered straight into
+    one packed buffer ``[T_total, D]`` in rank order -- no padding rows, no
+    compaction -- by one broadcast per owner, together with their lengths.
+    While the transfers run, the rank's queries are scored against its OWN
+    documents, then against every other shard as soon as it has landed.  All
+    launches write into one ``[Nq_local, Nb_total]`` score matrix (document
+    columns in rank order, so diagonal targets are ``rank_query_offset +
+    arange``).
 
     Backward, ``exchange="owner"`` (default): ``grad_queries`` is computed
     where the queries are.  For ``grad_documents`` one kernel regroups the
@@ -31,6 +32,12 @@ Contrastive training
 
     ``exchange="reduce_scatter"``: every rank routes a partial
     ``grad_documents`` for the whole buffer and the sums are reduce-scattered.
+
+    The transfers only overlap with the kernels if their own kernels find free
+    SMs: forward launches that run beside a transfer leave ``COLLECTIVE_SMS``
+    SMs unused; a process group created with
+    ``opts = ProcessGroupNCCL.Options(is_high_priority_stream=True);
+    opts.config.max_ctas = COLLECTIVE_SMS`` keeps its collectives within them.
 
 Both drivers take the operator namespace as a parameter so that their
 sharding / reassembly logic can be exercised on CPU ``gloo`` ranks with a
@@ -118,6 +125,11 @@ def score_candidates_padded_sharded(queries, documents, query_lengths, doc_lengt
 # Contrastive training: all-gather documents, per-owner gradient reduction
 # ---------------------------------------------------------------------------
 
+# SMs a forward launch leaves to the kernels of the transfers that run beside it.  A process
+# group whose collectives use more CTAs than this (ProcessGroupNCCL.Options().config.max_ctas)
+# still makes progress, with the CTAs that found room.
+COLLECTIVE_SMS = 8
+
 _INT_TABLES = {}
 
 
@@ -187,6 +199,26 @@ def _all_gather_rows(out: torch.Tensor, local: torch.Tensor, counts: Sequence[in
     return _Done()
 
 
+def _broadcast_rows(out: torch.Tensor, local: torch.Tensor, counts: Sequence[int], group, rank: int):
+    """Gather every rank's ``local [counts[r], ...]`` into ``out [sum(counts),
+    ...]`` in rank order as one broadcast per rank, issued in rank order on
+    every rank; returns the handles in rank order, so that a consumer can wait
+    for one piece at a time.  The own piece is copied."""
+    views = list(out.split(list(counts), dim=0))
+    local = local.contiguous()
+    handles = []
+    for r in range(len(counts)):
+        src = dist.get_global_rank(group, r) if group is not None else r
+        if counts[r] == 0:
+            handles.append(_Done())
+        elif r == rank:
+            handles.append(dist.broadcast(local, src=src, group=group, async_op=True))
+            views[r].copy_(local)
+        else:
+            handles.append(dist.broadcast(views[r], src=src, group=group, async_op=True))
+    return handles
+
+
 def _reduce_scatter_rows(full: torch.Tensor, counts: Sequence[int], rank: int, group) -> torch.Tensor:
     """Sum ``full [sum(counts), D]`` over the ranks and return this rank's rows
     ``[counts[rank], D]``.  NCCL reduce-scatters (ragged shards through a padded
@@ -216,12 +248,13 @@ def _offsets(ops, lengths: torch.Tensor) -> torch.Tensor:
 
 class _ShardedContrastive(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, queries, documents, doc_lengths, group, ops, exchange, shard_sizes):
+    def forward(ctx, queries, documents, doc_lengths, group, ops, exchange, shard_sizes, records_group):
         rank, world = _world(group)
         q = queries.contiguous()
         d_local = documents.contiguous()
         lens_local = doc_lengths.to(torch.int32).contiguous()
         ctx.group, ctx.ops, ctx.rank, ctx.world, ctx.exchange = group, ops, rank, world, exchange
+        ctx.records_group = records_group if records_group is not None else group
         if world == 1:
             offsets = _offsets(ops, lens_local)
             scores, argmax = ops.maxsim_contrastive_forward_with_argmax(q, d_local, offsets)
@@ -235,36 +268,46 @@ class _ShardedContrastive(torch.autograd.Function):
         col0 = [sum(n_docs[:r]) for r in range(world + 1)]
         nb_total, t_total = col0[-1], sum(tokens)
 
-        # start the exchanges: documents, their lengths and (for the owner exchange of the
-        # backward pass) the queries
+        # start the exchanges: the documents' lengths, the documents themselves -- one
+        # broadcast per owner, so that every shard can be scored as soon as it has landed --
+        # and (for the owner exchange of the backward pass) the queries
         docs_all = torch.empty((t_total, d_local.shape[1]), dtype=d_local.dtype, device=dev)
         lens_all = torch.empty((nb_total,), dtype=torch.int32, device=dev)
         h_lens = _all_gather_rows(lens_all, lens_local, n_docs, group, rank)
-        h_docs = _all_gather_rows(docs_all, d_local, tokens, group, rank)
+        h_docs = _broadcast_rows(docs_all, d_local, tokens, group, rank)
         q_all, h_q = None, None
         if exchange == "owner":
             q_all = torch.empty((sum(n_queries),) + tuple(q.shape[1:]), dtype=q.dtype, device=dev)
             h_q = _all_gather_rows(q_all, q, n_queries, group, rank)
 
-        # this rank's own documents are scored while the exchange runs
+        # This rank's own documents are scored while the exchange runs, then every other
+        # rank's shard as it arrives.  The forward kernel is persistent: it leaves a few SMs
+        # unused while transfers are still under way, or their kernels would only start
+        # when it ends.
         block = getattr(ops, "contrastive_forward_block", None)
         off_local = _offsets(ops, lens_local)
         scores = argmax = None
         if block is not None and q.is_cuda:
             scores = torch.empty((q.shape[0], nb_total), dtype=torch.float32, device=dev)
             argmax = torch.empty((q.shape[0], nb_total, q.shape[1]), dtype=torch.int32, device=dev)
-            if not block(q, d_local, off_local, scores, argmax, col0[rank], tokens[rank]):
+            if not block(q, d_local, off_local, scores, argmax, col0[rank], tokens[rank],
+                         reserve_sms=COLLECTIVE_SMS):
                 scores = argmax = None  # shape outside the kernel: one ordinary call below
         h_lens.wait()
-        h_docs.wait()
         offsets = _offsets(ops, lens_all)
+        others = [r for r in range(world) if r != rank and n_docs[r] > 0]
         if scores is None:
+            for h in h_docs:
+                h.wait()
             scores, argmax = ops.maxsim_contrastive_forward_with_argmax(q, docs_all, offsets)
         else:
-            for c_lo, c_hi in ((0, col0[rank]), (col0[rank + 1], nb_total)):
-                if c_hi > c_lo:
-                    n_tok = sum(tokens[r] for r in range(world) if c_lo <= col0[r] < c_hi)
-                    block(q, docs_all, offsets[c_lo:c_hi + 1], scores, argmax, c_lo, n_tok)
+            for k, r in enumerate(others):
+                h_docs[r].wait()
+                last = k + 1 == len(others)
+                block(q, docs_all, offsets[col0[r]:col0[r + 1] + 1], scores, argmax, col0[r], tokens[r],
+                      reserve_sms=0 if last else COLLECTIVE_SMS)
+            for h in h_docs:
+                h.wait()  # (shards without documents)
         ctx.save_for_backward(q, docs_all, offsets, argmax, d_local, off_local)
         ctx.q_all, ctx.h_q = q_all, h_q
         ctx.tokens, ctx.n_docs, ctx.n_queries, ctx.col0 = tokens, n_docs, n_queries, col0
@@ -274,15 +317,15 @@ class _ShardedContrastive(torch.autograd.Function):
     def backward(ctx, dscore):
         ops, group, rank, world = ctx.ops, ctx.group, ctx.rank, ctx.world
         g = dscore.contiguous().to(torch.float32)
-        none5 = (None,) * 5
+        no_grad = (None,) * 6
         if world == 1:
             q, d_local, offsets, argmax = ctx.saved_tensors
             dq, dd = ops.maxsim_contrastive_backward(g, q, d_local, offsets, argmax)
-            return (dq, dd) + none5
+            return (dq, dd) + no_grad
         q, docs_all, offsets, argmax, d_local, off_local = ctx.saved_tensors
         if ctx.exchange == "reduce_scatter":
             dq, dd_all = ops.maxsim_contrastive_backward(g, q, docs_all, offsets, argmax)
-            return (dq, _reduce_scatter_rows(dd_all, ctx.tokens, rank, group)) + none5
+            return (dq, _reduce_scatter_rows(dd_all, ctx.tokens, rank, group)) + no_grad
 
         # "owner".  The records of this rank's pairs go to the owners of the documents ...
         n_docs, n_queries, col0 = ctx.n_docs, ctx.n_queries, ctx.col0
@@ -297,7 +340,8 @@ class _ShardedContrastive(torch.autograd.Function):
         in_splits = [n * nq_local * width for n in n_docs]
         out_splits = [n_docs[rank] * nq * width for nq in n_queries]
         recv = torch.empty((sum(out_splits),), dtype=torch.int32, device=g.device)
-        h_rec = dist.all_to_all_single(recv, send, out_splits, in_splits, group=group, async_op=True)
+        h_rec = dist.all_to_all_single(recv, send, out_splits, in_splits, group=ctx.records_group,
+                                       async_op=True)
 
         # ... while grad_queries is computed here, where the queries are
         native = getattr(ops, "contrastive_backward_native", None)
@@ -325,11 +369,11 @@ class _ShardedContrastive(torch.autograd.Function):
                 dd = part(g_own, q_all, d_local, off_local, a_own, want_queries=False, want_documents=True)[1]
             else:
                 dd = ops.maxsim_contrastive_backward(g_own, q_all, d_local, off_local, a_own)[1]
-        return (dq, dd) + none5
+        return (dq, dd) + no_grad
 
 
 def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, ops=None,
-                              exchange: str = "owner", shard_sizes=None):
+                              exchange: str = "owner", shard_sizes=None, records_group=None):
     """Differentiable contrastive scores of this rank's queries against the
     documents of all ranks.
 
@@ -346,6 +390,12 @@ def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, op
     tokens, documents, queries)`` in rank order (a data pipeline can exchange
     these numbers ahead of the step): the driver then neither exchanges them
     nor waits for the device, so the host keeps launching ahead of the GPU.
+
+    ``records_group``, when given, is a second process group over the same
+    ranks that carries the all-to-all of the backward pass.  The forward
+    transfers run beside kernels and want a group limited to a few CTAs (see
+    the module text); the all-to-all has little to run beside and is fastest
+    on a group with NCCL's default CTA count.
 
     ``exchange`` selects how the backward pass gets that sum to the owner:
     ``"owner"`` (default) sends each owner the argmax and score gradient of its
@@ -365,7 +415,8 @@ def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, op
         raise TypeError(f"queries and documents must share dtype; got {queries.dtype} and {documents.dtype}")
     if exchange not in ("owner", "reduce_scatter"):
         raise ValueError(f"exchange must be 'owner' or 'reduce_scatter'; got {exchange!r}")
-    return _ShardedContrastive.apply(queries, documents, doc_lengths, group, ops, exchange, shard_sizes)
+    return _ShardedContrastive.apply(queries, documents, doc_lengths, group, ops, exchange, shard_sizes,
+                                     records_group)
 
 
 def contrastive_targets(n_queries_local: int, *, group=None, device=None,

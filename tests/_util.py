@@ -71,20 +71,22 @@ def assert_argmax(got, want, gaps, dtype: str, valid=None, what="argmax"):
 
 
 def assert_grads(got, want, dtype: str, what="grad"):
+    """Gradients against the oracle at the stated tolerance (2e-2 relative /
+    1e-2 absolute for fp16 / bf16, 1e-5 / 1e-5 for fp32), element by element."""
     got = np.asarray(got, dtype=np.float32)
     want = np.asarray(want, dtype=np.float32)
     assert got.shape == want.shape
     tol = SCORE_TOL[dtype]
     fin = np.isfinite(want)
     assert np.array_equal(np.isfinite(got), fin), f"{what}: finite pattern differs"
-    scale = max(1.0, float(np.abs(want[fin]).max())) if fin.any() else 1.0
     err = np.abs(got[fin] - want[fin])
-    # gradients are sums of up to hundreds of routed rows: the absolute term
-    # scales with the largest magnitude so fp32 add-order noise is tolerated
-    bound = tol["atol"] * scale + tol["rtol"] * np.abs(want[fin])
+    bound = tol["atol"] + tol["rtol"] * np.abs(want[fin])
+    if dtype == "fp32":
+        # sums of hundreds of fp32 products in a different order than the oracle's float64:
+        # the absolute term follows the magnitude of the sums
+        bound = bound + 1e-6 * (float(np.abs(want[fin]).max()) if fin.any() else 0.0)
     bad = err > bound
     assert not bad.any(), f"{what}: {bad.sum()} of {bad.size} outside tolerance; max err {err.max():.3e}"
-
 
 # ---------------------------------------------------------------------------
 # fp32 einsum checker on the GPU (tests only): the reference's formulation,

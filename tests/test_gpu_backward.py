@@ -298,3 +298,41 @@ def test_grad_queries_alone_with_argmax_entries_outside_their_document(dtype):
     wq, _ = oracle.contrastive_backward(f32(w[sel]), f32(q[sel]), f32(d), i64(off), a.cpu().numpy()[sel])
     assert_grads(f32(dq[sel]), wq, NAME_OF[dtype])
     assert _ops.device_status() == 0
+
+
+@pytest.mark.parametrize("dim", [96, 64, 32, 8])
+@pytest.mark.parametrize("layout", ["contrastive", "padded"])
+def test_grad_queries_with_32_or_more_routed_candidates_and_narrow_rows(dim, layout):
+    """Blocks of 32 candidates that are all routed take a path of the gather
+    kernel without per-row checks; with dim < 128 some lanes of a half-warp
+    have no element of the row and must still take part in the warp vote."""
+    g = torch.Generator().manual_seed(dim)
+    dt = torch.bfloat16
+    if layout == "contrastive":
+        Nq, Lq, Nb = 6, 16, 70
+        q = torch.randn(Nq, Lq, dim, generator=g).to(DEV, dt)
+        lens = torch.randint(3, 40, (Nb,), generator=g)
+        d = torch.randn(int(lens.sum()), dim, generator=g).to(DEV, dt)
+        off = torch.zeros(Nb + 1, dtype=torch.int32)
+        off[1:] = lens.cumsum(0)
+        off = off.to(DEV)
+        w = torch.randn(Nq, Nb, generator=g).to(DEV)
+        _, a = maxsim.score_contrastive_with_argmax(q, d, off)
+        dq, dd = _ops.ops.maxsim_contrastive_backward(w, q, d, off, a)
+        wq, wd = oracle.contrastive_backward(f32(w), f32(q), f32(d), i64(off), a.cpu().numpy())
+    else:
+        B, C, Lq, Ld = 3, 65, 16, 30
+        q = torch.randn(B, Lq, dim, generator=g).to(DEV, dt)
+        d = torch.randn(B, C, Ld, dim, generator=g).to(DEV, dt)
+        ql = torch.full((B,), Lq, dtype=torch.int32, device=DEV)
+        dl = torch.randint(1, Ld + 1, (B, C), generator=g, dtype=torch.int32).to(DEV)
+        w = torch.randn(B, C, generator=g).to(DEV)
+        _, a = maxsim.score_candidates_padded_with_argmax(q, d, ql, dl)
+        dq, dd = _ops.ops.maxsim_padded_backward(w.reshape(-1), q.reshape(B * Lq, dim),
+                                                 d.reshape(B * C * Ld, dim), ql, dl.reshape(-1),
+                                                 a.reshape(B * C, Lq), Lq, Ld, C)
+        wq, wd = oracle.candidates_padded_backward(f32(w), f32(q), f32(d), i64(ql), i64(dl), a.cpu().numpy())
+        dq, dd = dq.view(B, Lq, dim), dd.view(B, C, Ld, dim)
+    assert_grads(f32(dq), wq, "bf16")
+    assert_grads(f32(dd), wd, "bf16")
+    assert _ops.device_status() == 0

@@ -79,6 +79,30 @@ def test_tc05_query_lengths_and_dims(Lq, dim, dtype, path):
         _check(q, d, off, dtype)
 
 
+@pytest.mark.parametrize("Lq,dim", [(64, 96), (16, 64), (48, 128), (32, 128)])
+@pytest.mark.parametrize("path", [8, 9])
+def test_tc05_many_items_per_cta(Lq, dim, path):
+    """More work items than SMs, several documents per item: every CTA walks its
+    item loop many times (query block reloads, barrier phases that wrap, the
+    hand-over ring of queries that span two warps)."""
+    _ops.set_forward_path(path)
+    g = torch.Generator().manual_seed(Lq + dim)
+    d_lens = torch.randint(1, 90, (700,), generator=g).tolist()
+    q, d, off = _make(640, d_lens, torch.bfloat16, 23, Lq=Lq, dim=dim)
+    s, a = maxsim.score_contrastive_with_argmax(q, d, off)
+    s0 = maxsim.score_contrastive(q, d, off)
+    sel = torch.arange(0, 640, 97)
+    ws, wa, gaps = oracle.score_contrastive(f32(q[sel]), f32(d), i64(off), want_gap=True)
+    assert_scores(f32(s[sel]), ws, "bf16")
+    assert_scores(f32(s0[sel]), ws, "bf16")
+    assert_argmax(a[sel].cpu().numpy(), wa, gaps, "bf16")
+    # every pair against the streaming kernel
+    _ops.set_forward_path(2)
+    s_mma, a_mma = maxsim.score_contrastive_with_argmax(q, d, off)
+    torch.testing.assert_close(s, s_mma, rtol=1e-4, atol=2e-3)
+    assert (a != a_mma).float().mean() < 2e-3
+
+
 @pytest.mark.parametrize("path", [8, 9])
 @pytest.mark.parametrize("Lq", [16, 32, 64])
 def test_tc05_large_and_negative_maxima_take_the_exact_walk(path, Lq):
