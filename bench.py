@@ -642,7 +642,9 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
         shard_sizes.append((int(lens_host[a0:a1].sum()), a1 - a0, a1 - a0))
 
     # the record exchange of the backward pass on a group with NCCL's default CTA count
-    records_group = dist.new_group(backend="nccl")
+    records_group = dist.new_group(
+        backend="nccl",
+        pg_options=dist.ProcessGroupNCCL.Options(is_high_priority_stream=True))
 
     def one_step(exchange, sizes, keep=False):
         q.grad = None

@@ -294,7 +294,6 @@ fwd_tc05_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   static_assert(LQP == 16 || LQP == 32 || LQP == 64, "lanes per query");
   static_assert(kThreads == 384, "register hand-over is sized for 12 warps");
   constexpr int kQPerSub = kBM / LQP;          // queries per accumulator
-  constexpr int kQPerCta = kQPerSub * kMSub;
   extern __shared__ unsigned char tc05_smem_raw[];
   const uint32_t raw_base = smem_u32(tc05_smem_raw);
   const uint32_t base = (raw_base + 1023u) & ~1023u;
