@@ -646,11 +646,27 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
         backend="nccl",
         pg_options=dist.ProcessGroupNCCL.Options(is_high_priority_stream=True))
 
-    def one_step(exchange, sizes, keep=False):
+    # exchange buffers in peer-mapped memory (all ranks on one node); if the mapping cannot be
+    # set up here the collective transport alone is measured and the reason is reported
+    peer, peer_error = None, None
+    try:
+        from maxsim_b200.peer import PeerExchange
+        peer = PeerExchange(max_doc_tokens=max(s[0] for s in shard_sizes),
+                            max_docs=max(s[1] for s in shard_sizes),
+                            max_queries=max(s[2] for s in shard_sizes),
+                            lq=q.shape[1], dim=q.shape[2], dtype=q.dtype)
+    except Exception as exc:  # noqa: BLE001 -- reported in the record
+        peer_error = f"{type(exc).__name__}: {exc}"[:300]
+    have = torch.tensor([1 if peer is not None else 0], device=dev)
+    dist.all_reduce(have, op=dist.ReduceOp.MIN)
+    if not bool(have.item()):
+        peer = None
+
+    def one_step(exchange, sizes, keep=False, transport=None):
         q.grad = None
         d.grad = None
         s = mdist.score_contrastive_sharded(q, d, lens, exchange=exchange, shard_sizes=sizes,
-                                            records_group=records_group)
+                                            records_group=records_group, peer=transport)
         if keep:
             s.retain_grad()
         # every rank averages over its own queries; the global mean is over all n
@@ -659,8 +675,8 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
         return s, loss
 
     # --- parity of the sharded step
-    def check(exchange, sizes):
-        s, loss = one_step(exchange, sizes, keep=True)
+    def check(exchange, sizes, transport=None):
+        s, loss = one_step(exchange, sizes, keep=True, transport=transport)
         g = s.grad
         sums = torch.stack([(g.double() * s.detach().double()).sum(),
                             (q.grad.double() * q.detach().double()).sum(),
@@ -692,24 +708,36 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
     same = torch.tensor([1 if torch.equal(s_owner, s_rs) else 0], device=dev)
     dist.all_reduce(same, op=dist.ReduceOp.MIN)
     parity_ok = par_owner["ok_all_ranks"] and par_rs["ok_all_ranks"] and bool(same.item())
+    par_peer = None
+    if peer is not None:
+        par_peer, s_peer = check("owner", shard_sizes, peer)
+        same_p = torch.tensor([1 if torch.equal(s_owner, s_peer) else 0], device=dev)
+        dist.all_reduce(same_p, op=dist.ReduceOp.MIN)
+        status = torch.tensor([_ops_status()], device=dev)
+        dist.all_reduce(status, op=dist.ReduceOp.MAX)
+        par_peer["device_status_all_ranks"] = int(status.item())
+        parity_ok = (parity_ok and par_peer["ok_all_ranks"] and bool(same_p.item())
+                     and int(status.item()) == 0)
 
-    def timed(exchange, sizes=None):
+    def timed(exchange, sizes=None, transport=None):
         for _ in range(3):
-            one_step(exchange, sizes)
+            one_step(exchange, sizes, transport=transport)
         torch.cuda.synchronize()
         dist.barrier()
         iters = 10
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for _ in range(iters):
-            one_step(exchange, sizes)
+            one_step(exchange, sizes, transport=transport)
         e1.record()
         torch.cuda.synchronize()
         return reduce_max(e0.elapsed_time(e1) / iters)
 
     ms_rs = timed("reduce_scatter")
     ms_owner = timed("owner")
-    ms = timed("owner", shard_sizes)
+    ms_nccl = timed("owner", shard_sizes)
+    ms_peer = timed("owner", shard_sizes, peer) if peer is not None else None
+    ms = ms_peer if ms_peer is not None else ms_nccl
     T = int(full["doc_lengths_all"].sum().item())
     flops = 2 * 128 * n * 32 * T + 4 * 128 * n * n * 32
     return {"c5_contrastive_train_bf16_sharded": {
@@ -718,18 +746,30 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
         "efficiency": ms_single / ms / world,
         "tensor_frac_all_gpus": flops / (ms * 1e-3) / (world * peaks["bf16_tflops"] * 1e12),
         "parity_ok": parity_ok,
-        "parity": {"owner": par_owner, "reduce_scatter": par_rs,
+        "transport": "peer" if ms_peer is not None else "nccl",
+        "peer_transport_unavailable": peer_error,
+        "parity": {"owner": par_owner, "reduce_scatter": par_rs, "owner_peer_transport": par_peer,
                    "owner_and_reduce_scatter_scores_equal": bool(same.item())},
+        "ms_per_step_nccl": ms_nccl, "efficiency_nccl": ms_single / ms_nccl / world,
         "ms_per_step_sizes_exchanged_in_step": ms_owner,
         "ms_per_step_reduce_scatter": ms_rs,
         "efficiency_reduce_scatter": ms_single / ms_rs / world,
         "note": f"global Nq=Nb={n} over {world} ranks (strong scaling); ms_per_step: owner exchange "
                 "with every rank's shard sizes passed in (known to the data pipeline), so the host "
-                "never waits for the device; ms_per_step_sizes_exchanged_in_step: the sizes "
+                "never waits for the device, over the transport named in 'transport' -- 'peer': "
+                "shards fetched from peer-mapped buffers by the copy engines, argmax records stored "
+                "into the owners' memory by the regrouping kernel, one barrier kernel per pass; "
+                "'nccl' (always measured, ms_per_step_nccl): per-owner broadcasts and an all-to-all; "
+                "ms_per_step_sizes_exchanged_in_step (nccl): the sizes "
                 "all-gathered and read back inside the step; ms_per_step_reduce_scatter: fp32 "
                 "partial grad_documents reduce-scattered; single_gpu_ms_same_run: the whole problem "
                 "on one GPU in this run (every rank times it, the slowest counts); all times max "
                 "over ranks; rank 0's parity record is shown, parity_ok is the AND over ranks"}}
+
+
+def _ops_status() -> int:
+    from maxsim_b200 import _ops
+    return _ops.device_status()
 
 
 def bench_strong_scaling(dev, dist, rank, world, steps, weak_kernel_ms):
@@ -1084,7 +1124,8 @@ def run_gpu_arm(args):
                 short = {}
                 for key in ("ms_per_step", "forward_ms", "tensor_frac", "forward_tensor_frac",
                             "forward_unique_doc_hbm_frac", "step_hbm_frac", "single_gpu_ms_same_run",
-                            "efficiency", "efficiency_reduce_scatter", "ms_per_step_reduce_scatter",
+                            "efficiency", "transport", "ms_per_step_nccl", "efficiency_nccl",
+                            "efficiency_reduce_scatter", "ms_per_step_reduce_scatter",
                             "parity_ok", "ms"):
                     if key in rec:
                         v = rec[key]

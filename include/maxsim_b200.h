@@ -360,6 +360,26 @@ MAXSIM_API int maxsim_contrastive_backward_documents_from_records(
     int64_t Nq, int64_t Lq, int64_t Nb, int64_t dim, int64_t total_d_tokens,
     int dtype, int native, void* stream);
 
+/* The same exchange over peer-mapped memory instead of a collective (no
+ * reference counterpart; the GPUs of one node map each other's buffers).
+ * pack_owner_records_to writes owner o's block straight to owner_blocks[o]
+ * (device array of n_owners device pointers, each into that owner's memory as
+ * mapped in this process, already advanced to where this rank's queries
+ * belong): the kernel's stores are the transfer.
+ * peer_barrier is the stream-ordered barrier that follows: flags (device
+ * array of `world` pointers, flags[r] = rank r's `world` flag words, zero
+ * before the first barrier) and an epoch that the caller raises by one per
+ * barrier, the same on all ranks.  Stores made on `stream` before the barrier
+ * are visible to a rank's kernels launched after its own barrier.  A rank
+ * waits at most `polls` polls (0: about ten seconds) for each peer; a wait
+ * that runs out sets bit 4 of the word maxsim_b200_device_status reports. */
+MAXSIM_API int maxsim_b200_pack_owner_records_to(const int32_t* argmax, const float* dscore,
+                                                 const int32_t* col_start,
+                                                 int32_t* const* owner_blocks, int64_t n_owners,
+                                                 int64_t Nq, int64_t Nb, int64_t Lq, void* stream);
+MAXSIM_API int maxsim_b200_peer_barrier(uint32_t* const* flags, int64_t rank, int64_t world,
+                                        uint32_t epoch, uint32_t polls, void* stream);
+
 /* Replaces maxsim_contrastive_backward (maxsim_cuda/maxsim.cu:1856-1920).
  * dscore [Nq, Nb]; grad_queries [Nq, Lq, dim], grad_documents
  * [total_d_tokens, dim].  Extension: either gradient pointer may be NULL, in

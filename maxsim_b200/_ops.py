@@ -66,6 +66,8 @@ _SIGNATURES = {
     "maxsim_contrastive_forward_with_argmax_block": (c_int, [_P] * 5 + [_I64] * 9 + [c_int, _P]),
     "maxsim_b200_pack_owner_records": (c_int, [_P] * 3 + [_I64] * 4 + [_P, _P]),
     "maxsim_contrastive_backward_documents_from_records": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, c_int, _P]),
+    "maxsim_b200_pack_owner_records_to": (c_int, [_P] * 4 + [_I64] * 4 + [_P]),
+    "maxsim_b200_peer_barrier": (c_int, [_P, _I64, _I64, ctypes.c_uint32, ctypes.c_uint32, _P]),
     "maxsim_padded_backward_native": (c_int, [_P] * 8 + [_I64] * 5 + [c_int, _P]),
     "maxsim_contrastive_backward_native": (c_int, [_P] * 7 + [_I64] * 5 + [c_int, _P]),
 }
@@ -804,6 +806,35 @@ def pack_owner_records(argmax, dscore, col_start) -> torch.Tensor:
             _ptr(a), _ptr(g), _ptr(cs), cs.shape[0] - 1, Nq, Nb, Lq, _ptr(send), _stream_ptr())
     _check(rc, "maxsim_b200_pack_owner_records")
     return send
+
+
+def pack_owner_records_to(argmax, dscore, col_start, owner_blocks) -> None:
+    """:func:`pack_owner_records` without the send buffer: owner ``o``'s block
+    is written to the address ``owner_blocks[o]`` (``[R]`` int64 on the device:
+    pointers into the owners' memory as mapped in this process)."""
+    dev = _require_cuda(argmax, dscore, col_start, owner_blocks)
+    a = argmax.contiguous()
+    g = dscore.contiguous().to(torch.float32)
+    cs = _i32(col_start)
+    if owner_blocks.dtype != torch.int64 or owner_blocks.numel() != cs.shape[0] - 1:
+        raise ValueError("owner_blocks must hold one int64 address per owner")
+    Nq, Nb, Lq = a.shape
+    with _on_device(dev):
+        rc = load_library().maxsim_b200_pack_owner_records_to(
+            _ptr(a), _ptr(g), _ptr(cs), owner_blocks.data_ptr(), cs.shape[0] - 1, Nq, Nb, Lq,
+            _stream_ptr())
+    _check(rc, "maxsim_b200_pack_owner_records_to")
+
+
+def peer_barrier(flags, rank: int, world: int, epoch: int, polls: int = 0) -> None:
+    """Stream-ordered barrier between the ranks of a node over flag words in
+    peer-mapped memory (``flags``: ``[world]`` int64 addresses on the device,
+    see the header); ``epoch`` grows by one per barrier on every rank."""
+    dev = _require_cuda(flags)
+    with _on_device(dev):
+        rc = load_library().maxsim_b200_peer_barrier(
+            flags.data_ptr(), int(rank), int(world), int(epoch) & 0xFFFFFFFF, int(polls), _stream_ptr())
+    _check(rc, "maxsim_b200_peer_barrier")
 
 
 def contrastive_backward_documents_from_records(records, queries, documents, document_offsets):

@@ -208,9 +208,18 @@ int run_forward(const PairTable& t, float* scores, int32_t* argmax, int dtype, v
 template <typename T, int LAYOUT>
 int launch_dq16(const PairTable& t, const float* dscore, const int32_t* argmax, void* dq,
                 int64_t q_rows, int native, cudaStream_t st) {
-  const int64_t grid = (q_rows + kBwdWarps - 1) / kBwdWarps;
-  bwd_dq_gather16_kernel<T, LAYOUT><<<(unsigned)grid, kBwdWarps * 32, 0, st>>>(t, dscore, argmax, dq,
-                                                                              q_rows, native);
+  // One warp per row fills the GPU from about three waves of warps up (36 resident per SM);
+  // with fewer rows and enough candidates, 2 or 4 warps share a row.
+  const int64_t full = (int64_t)sm_count() * 36 * 3;
+  const int split = (q_rows >= full || t.C < 256) ? 1 : (2 * q_rows >= full || t.C < 512) ? 2 : 4;
+  const int64_t grid = (q_rows * split + kBwdWarps - 1) / kBwdWarps;
+  const unsigned threads = kBwdWarps * 32;
+  if (split == 1)
+    bwd_dq_gather16_kernel<T, LAYOUT, 1><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq, q_rows, native);
+  else if (split == 2)
+    bwd_dq_gather16_kernel<T, LAYOUT, 2><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq, q_rows, native);
+  else
+    bwd_dq_gather16_kernel<T, LAYOUT, 4><<<(unsigned)grid, threads, 0, st>>>(t, dscore, argmax, dq, q_rows, native);
   return launch_check("bwd_dq_gather16_kernel");
 }
 
@@ -922,14 +931,16 @@ int maxsim_contrastive_forward_with_argmax_block(
   return run_forward<kContrastive, true>(t, scores, argmax, dtype, stream);
 }
 
-int maxsim_b200_pack_owner_records(const int32_t* argmax, const float* dscore,
-                                   const int32_t* col_start, int64_t n_owners, int64_t Nq,
-                                   int64_t Nb, int64_t Lq, int32_t* send, void* stream) {
+namespace {
+int launch_pack_owner_records(const int32_t* argmax, const float* dscore, const int32_t* col_start,
+                              int64_t n_owners, int64_t Nq, int64_t Nb, int64_t Lq, int32_t* send,
+                              int32_t* const* owner_blocks, void* stream) {
   if (n_owners <= 0 || Nq < 0 || Nb < 0 || Lq <= 0 || !fits_i32(Nq) || !fits_i32(Nb) ||
       !fits_i32(Lq) || !fits_i32(n_owners))
     return fail(MAXSIM_EINVAL, "sizes must be >= 0 (Lq, n_owners > 0) and fit int32");
   if (Nq * Nb == 0) return MAXSIM_OK;
-  if (!argmax || !dscore || !col_start || !send) return fail(MAXSIM_EINVAL, "null pointer argument");
+  if (!argmax || !dscore || !col_start || (!send && !owner_blocks))
+    return fail(MAXSIM_EINVAL, "null pointer argument");
   if (n_owners > 65535) return fail(MAXSIM_EINVAL, "too many owners");
   // about one wave of CTAs over all owners, each thread copying several words
   int64_t gx = ((int64_t)sm_count() * 8 + n_owners - 1) / n_owners;
@@ -937,8 +948,36 @@ int maxsim_b200_pack_owner_records(const int32_t* argmax, const float* dscore,
   if (gx > need) gx = need > 0 ? need : 1;
   dim3 grid((unsigned)gx, (unsigned)n_owners);
   pack_owner_records_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      argmax, dscore, col_start, (int)Nq, (int)Nb, (int)Lq, send);
+      argmax, dscore, col_start, (int)Nq, (int)Nb, (int)Lq, send, owner_blocks);
   return launch_check("pack_owner_records_kernel");
+}
+}  // namespace
+
+int maxsim_b200_pack_owner_records(const int32_t* argmax, const float* dscore,
+                                   const int32_t* col_start, int64_t n_owners, int64_t Nq,
+                                   int64_t Nb, int64_t Lq, int32_t* send, void* stream) {
+  return launch_pack_owner_records(argmax, dscore, col_start, n_owners, Nq, Nb, Lq, send, nullptr,
+                                   stream);
+}
+
+int maxsim_b200_pack_owner_records_to(const int32_t* argmax, const float* dscore,
+                                      const int32_t* col_start, int32_t* const* owner_blocks,
+                                      int64_t n_owners, int64_t Nq, int64_t Nb, int64_t Lq,
+                                      void* stream) {
+  return launch_pack_owner_records(argmax, dscore, col_start, n_owners, Nq, Nb, Lq, nullptr,
+                                   owner_blocks, stream);
+}
+
+int maxsim_b200_peer_barrier(uint32_t* const* flags, int64_t rank, int64_t world, uint32_t epoch,
+                             uint32_t polls, void* stream) {
+  if (world <= 0 || world > 1024 || rank < 0 || rank >= world)
+    return fail(MAXSIM_EINVAL, "rank / world out of range");
+  if (world == 1) return MAXSIM_OK;
+  if (!flags) return fail(MAXSIM_EINVAL, "null pointer argument");
+  const unsigned threads = (unsigned)((world + 31) / 32 * 32);
+  peer_barrier_kernel<<<1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      flags, (int)rank, (int)world, epoch, polls ? polls : (1u << 24));
+  return launch_check("peer_barrier_kernel");
 }
 
 int maxsim_contrastive_backward_documents_from_records(

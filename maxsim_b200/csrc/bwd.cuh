@@ -199,19 +199,26 @@ bwd_dq_gather_kernel(PairTable t, const float* __restrict__ dscore,
 // for this kernel -- 16-byte reads of random rows keep the shared-memory pipe
 // busier than L2 was, with one barrier per document on top.
 // ---------------------------------------------------------------------------
-template <typename T, int LAYOUT>
+// SPLIT > 1: that many warps of a block share a row, each taking every SPLIT-th block of 32
+// candidates, and add their sums through shared memory -- for launches with too few rows to
+// fill the GPU with one warp per row (a rank's share of the queries in a sharded step).
+template <typename T, int LAYOUT, int SPLIT>
 __global__ void __launch_bounds__(kBwdWarps * 32)
 bwd_dq_gather16_kernel(PairTable t, const float* __restrict__ dscore,
                        const int32_t* __restrict__ argmax, void* __restrict__ dq,
                        int64_t n_rows, int native) {
   static_assert(sizeof(T) == 2, "16-bit element types only");
+  static_assert(SPLIT == 1 || SPLIT == 2 || SPLIT == 4, "SPLIT divides the warps of a block");
   const int lane = threadIdx.x & 31, half = lane >> 4, hl = lane & 15;
-  const int64_t row = (int64_t)blockIdx.x * kBwdWarps + (threadIdx.x >> 5);
-  if (row >= n_rows) return;
+  const int warp = threadIdx.x >> 5;
+  const int64_t row = ((int64_t)blockIdx.x * kBwdWarps + warp) / SPLIT;
+  const int part = SPLIT > 1 ? warp % SPLIT : 0;
+  const bool row_ok = row < n_rows;
+  if (SPLIT == 1 && !row_ok) return;
   const int dim = t.dim, slots = t.q_slots, C = t.C;
   const int64_t b = row / slots;
   const int i = (int)(row - b * slots);
-  const int Lq = (LAYOUT == kPadded) ? __ldg(t.ia + b) : slots;
+  const int Lq = (LAYOUT == kPadded) ? ((SPLIT == 1 || row_ok) ? __ldg(t.ia + b) : 0) : slots;
   const T* D = reinterpret_cast<const T*>(t.documents);
   const int k = hl * 8;
   const bool k_ok = k < dim;
@@ -223,8 +230,8 @@ bwd_dq_gather16_kernel(PairTable t, const float* __restrict__ dscore,
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
 
-  if (i < Lq) {
-    for (int c0 = 0; c0 < C; c0 += 32) {
+  if ((SPLIT == 1 || row_ok) && i < Lq) {
+    for (int c0 = part * 32; c0 < C; c0 += 32 * SPLIT) {
       const int c = c0 + lane;
       float gl = 0.f;
       int32_t src = -1;  // winning document row of candidate c0+lane, or -1
@@ -286,6 +293,21 @@ bwd_dq_gather16_kernel(PairTable t, const float* __restrict__ dscore,
   }
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 16);
+  if constexpr (SPLIT > 1) {
+    __shared__ float partial[kBwdWarps][16][8];
+    if (part != 0 && half == 0) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) partial[warp][hl][e] = acc[e];
+    }
+    __syncthreads();
+    if (part != 0 || !row_ok) return;
+    if (half == 0) {
+#pragma unroll
+      for (int w = 1; w < SPLIT; ++w)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] += partial[warp + w][hl][e];
+    }
+  }
   if (half == 0 && k_ok) {
     void* row_base = native ? static_cast<void*>(reinterpret_cast<T*>(dq) + row * dim)
                             : static_cast<void*>(reinterpret_cast<float*>(dq) + row * dim);
@@ -1028,15 +1050,18 @@ bwd_dd_invert_kernel(PairTable t, const float* __restrict__ dscore,
 // One thread per word of `send`; blockIdx.y is the owner, so that its column
 // range is uniform over the block and both sides of the copy are coalesced.
 // ---------------------------------------------------------------------------
+// With `owner_blocks` the block of owner o is written to owner_blocks[o] instead: the
+// pointers are into the owners' own memory (peer mappings), so the kernel's stores are the
+// transfer and no send buffer or all-to-all exists.
 __global__ void __launch_bounds__(256)
 pack_owner_records_kernel(const int32_t* __restrict__ argmax, const float* __restrict__ dscore,
                           const int32_t* __restrict__ col_start, int Nq, int Nb, int Lq,
-                          int32_t* __restrict__ send) {
+                          int32_t* __restrict__ send, int32_t* const* __restrict__ owner_blocks) {
   const int o = blockIdx.y;
   const int c0 = __ldg(col_start + o), n_o = __ldg(col_start + o + 1) - c0;
   const int rec = Lq + 1;
   const int64_t words = (int64_t)Nq * n_o * rec;          // of this owner's block
-  int32_t* dst = send + (int64_t)c0 * Nq * rec;
+  int32_t* dst = owner_blocks ? owner_blocks[o] : send + (int64_t)c0 * Nq * rec;
   const int64_t per_query = (int64_t)n_o * rec;
   for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < words;
        w += (int64_t)gridDim.x * blockDim.x) {
@@ -1045,6 +1070,36 @@ pack_owner_records_kernel(const int32_t* __restrict__ argmax, const float* __res
     const int dl = r / rec, slot = r - dl * rec;
     const int64_t pair = (int64_t)q * Nb + c0 + dl;
     dst[w] = slot < Lq ? __ldg(argmax + pair * Lq + slot) : __float_as_int(__ldg(dscore + pair));
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Barrier between the ranks of one node over flags in peer-mapped memory.
+// flags[r] points at rank r's flag words (one per rank) as mapped into this
+// process; thread t tells rank t that this rank has reached barrier `epoch`
+// (a release store at system scope into flags[t][rank], after the stream's
+// earlier stores to peer memory) and waits until rank t has said the same
+// (flags[rank][t] >= epoch; epochs only grow, so a peer that is already one
+// barrier ahead satisfies the wait too).  The wait is bounded: after `limit`
+// polls the kernel sets bit 4 of the status word and returns.
+// ---------------------------------------------------------------------------
+__global__ void peer_barrier_kernel(uint32_t* const* __restrict__ flags, int rank, int world,
+                                    uint32_t epoch, uint32_t limit) {
+  const int t = threadIdx.x;
+  if (t >= world || t == rank) return;
+  __threadfence_system();
+  uint32_t* theirs = flags[t] + rank;
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(theirs), "r"(epoch) : "memory");
+  const uint32_t* mine = flags[rank] + t;
+  for (uint32_t it = 0;; ++it) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+    if ((int32_t)(v - epoch) >= 0) break;
+    if (it >= limit) {
+      atomicOr(&g_device_status, 4);
+      break;
+    }
+    __nanosleep(200);
   }
 }
 

@@ -154,6 +154,18 @@ class _Done:
         return True
 
 
+class _AfterBarrier:
+    """Handle of an exchange made of stores to peer memory: it is complete on
+    every rank once the group's barrier has been passed on the stream."""
+
+    def __init__(self, peer):
+        self.peer = peer
+
+    def wait(self):
+        self.peer.barrier()
+        return True
+
+
 def _exchange_sizes(documents, lengths, n_queries, group, world, shard_sizes):
     """Every rank's ``(document tokens, documents, queries)`` in rank order."""
     if shard_sizes is not None:
@@ -248,7 +260,8 @@ def _offsets(ops, lengths: torch.Tensor) -> torch.Tensor:
 
 class _ShardedContrastive(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, queries, documents, doc_lengths, group, ops, exchange, shard_sizes, records_group):
+    def forward(ctx, queries, documents, doc_lengths, group, ops, exchange, shard_sizes, records_group,
+                peer=None):
         rank, world = _world(group)
         q = queries.contiguous()
         d_local = documents.contiguous()
@@ -267,6 +280,9 @@ class _ShardedContrastive(torch.autograd.Function):
         n_queries = [s[2] for s in sizes]
         col0 = [sum(n_docs[:r]) for r in range(world + 1)]
         nb_total, t_total = col0[-1], sum(tokens)
+        ctx.peer, ctx.sizes = peer, sizes
+        if peer is not None:
+            return _ShardedContrastive._forward_peer(ctx, q, d_local, lens_local, ops, peer, sizes, col0)
 
         # start the exchanges: the documents' lengths, the documents themselves -- one
         # broadcast per owner, so that every shard can be scored as soon as it has landed --
@@ -314,10 +330,55 @@ class _ShardedContrastive(torch.autograd.Function):
         return scores
 
     @staticmethod
+    def _forward_peer(ctx, q, d_local, lens_local, ops, peer, sizes, col0):
+        """The forward pass over peer-mapped buffers (maxsim_b200.peer): no
+        collective; copies by the copy engines beside forward launches that keep
+        every SM."""
+        rank, world = ctx.rank, ctx.world
+        dev = q.device
+        tokens = [s[0] for s in sizes]
+        n_docs = [s[1] for s in sizes]
+        n_queries = [s[2] for s in sizes]
+        peer.check_fits(sizes, q.shape[1], q.shape[2], q.dtype)
+        docs_all = torch.empty((sum(tokens), d_local.shape[1]), dtype=d_local.dtype, device=dev)
+        lens_all = torch.empty((col0[-1],), dtype=torch.int32, device=dev)
+        q_all = torch.empty((sum(n_queries),) + tuple(q.shape[1:]), dtype=q.dtype, device=dev)
+        lens_event, doc_events, q_event, order = peer.gather(d_local, lens_local, q, sizes, docs_all,
+                                                             lens_all, q_all)
+        main = torch.cuda.current_stream(dev)
+        off_local = _offsets(ops, lens_local)
+        scores = torch.empty((q.shape[0], col0[-1]), dtype=torch.float32, device=dev)
+        argmax = torch.empty((q.shape[0], col0[-1], q.shape[1]), dtype=torch.int32, device=dev)
+        blocks = ops.contrastive_forward_block(q, d_local, off_local, scores, argmax, col0[rank],
+                                               tokens[rank])
+        main.wait_event(lens_event)
+        offsets = _offsets(ops, lens_all)
+        if blocks:
+            # the shards arrive in ring order: those after this rank's own, then those before
+            # it.  Each of the two runs is a contiguous range of columns and gets one launch
+            # (the copies are far quicker than the block scored meanwhile, and every launch
+            # pays its own ramp-up and tail).
+            for first, last in ((rank + 1, world), (0, rank)):
+                if col0[last] == col0[first]:
+                    continue
+                main.wait_event(doc_events[last - 1])  # the copies complete in the order issued
+                ops.contrastive_forward_block(q, docs_all, offsets[col0[first]:col0[last] + 1], scores,
+                                              argmax, col0[first], sum(tokens[first:last]))
+        else:  # shape outside the block kernel: one ordinary call over all shards
+            for r in order:
+                main.wait_event(doc_events[r])
+            scores, argmax = ops.maxsim_contrastive_forward_with_argmax(q, docs_all, offsets)
+        main.wait_event(q_event)  # every read of a peer's buffers is now ordered before what follows
+        ctx.save_for_backward(q, docs_all, offsets, argmax, d_local, off_local)
+        ctx.q_all, ctx.h_q = q_all, _Done()
+        ctx.tokens, ctx.n_docs, ctx.n_queries, ctx.col0 = tokens, n_docs, n_queries, col0
+        return scores
+
+    @staticmethod
     def backward(ctx, dscore):
         ops, group, rank, world = ctx.ops, ctx.group, ctx.rank, ctx.world
         g = dscore.contiguous().to(torch.float32)
-        no_grad = (None,) * 6
+        no_grad = (None,) * 7
         if world == 1:
             q, d_local, offsets, argmax = ctx.saved_tensors
             dq, dd = ops.maxsim_contrastive_backward(g, q, d_local, offsets, argmax)
@@ -331,17 +392,23 @@ class _ShardedContrastive(torch.autograd.Function):
         n_docs, n_queries, col0 = ctx.n_docs, ctx.n_queries, ctx.col0
         nq_local, lq = q.shape[0], q.shape[1]
         pack = getattr(ops, "pack_owner_records", None)
-        if pack is not None and g.is_cuda:
-            send = pack(argmax, g, _device_ints(col0, g.device))
-        else:
-            record = torch.cat([argmax.to(torch.int32), g.view(torch.int32).unsqueeze(-1)], dim=2)
-            send = torch.cat([record[:, col0[o]:col0[o + 1]].reshape(-1) for o in range(world)])
         width = lq + 1
-        in_splits = [n * nq_local * width for n in n_docs]
-        out_splits = [n_docs[rank] * nq * width for nq in n_queries]
-        recv = torch.empty((sum(out_splits),), dtype=torch.int32, device=g.device)
-        h_rec = dist.all_to_all_single(recv, send, out_splits, in_splits, group=ctx.records_group,
-                                       async_op=True)
+        peer = getattr(ctx, "peer", None)
+        if peer is not None:
+            # the regrouping kernel stores each owner's block in that owner's memory
+            recv = peer.send_records(argmax, g, _device_ints(col0, g.device), ctx.sizes)
+            h_rec = _AfterBarrier(peer)
+        else:
+            if pack is not None and g.is_cuda:
+                send = pack(argmax, g, _device_ints(col0, g.device))
+            else:
+                record = torch.cat([argmax.to(torch.int32), g.view(torch.int32).unsqueeze(-1)], dim=2)
+                send = torch.cat([record[:, col0[o]:col0[o + 1]].reshape(-1) for o in range(world)])
+            in_splits = [n * nq_local * width for n in n_docs]
+            out_splits = [n_docs[rank] * nq * width for nq in n_queries]
+            recv = torch.empty((sum(out_splits),), dtype=torch.int32, device=g.device)
+            h_rec = dist.all_to_all_single(recv, send, out_splits, in_splits, group=ctx.records_group,
+                                           async_op=True)
 
         # ... while grad_queries is computed here, where the queries are
         native = getattr(ops, "contrastive_backward_native", None)
@@ -373,7 +440,7 @@ class _ShardedContrastive(torch.autograd.Function):
 
 
 def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, ops=None,
-                              exchange: str = "owner", shard_sizes=None, records_group=None):
+                              exchange: str = "owner", shard_sizes=None, records_group=None, peer=None):
     """Differentiable contrastive scores of this rank's queries against the
     documents of all ranks.
 
@@ -397,6 +464,13 @@ def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, op
     the module text); the all-to-all has little to run beside and is fastest
     on a group with NCCL's default CTA count.
 
+    ``peer``, when given, is a :class:`maxsim_b200.peer.PeerExchange` built
+    for this group: the shards then travel as copies out of peer-mapped
+    buffers (copy engines; the forward launches keep every SM) and the argmax
+    records as stores of the regrouping kernel into the owners' memory, with
+    one barrier kernel per pass instead of collectives.  Needs
+    ``shard_sizes``, ``exchange="owner"`` and CUDA tensors.
+
     ``exchange`` selects how the backward pass gets that sum to the owner:
     ``"owner"`` (default) sends each owner the argmax and score gradient of its
     documents and lets it compute the gradient from the all-gathered queries;
@@ -415,8 +489,13 @@ def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, op
         raise TypeError(f"queries and documents must share dtype; got {queries.dtype} and {documents.dtype}")
     if exchange not in ("owner", "reduce_scatter"):
         raise ValueError(f"exchange must be 'owner' or 'reduce_scatter'; got {exchange!r}")
+    if peer is not None:
+        if exchange != "owner" or shard_sizes is None or not queries.is_cuda:
+            raise ValueError("the peer transport needs exchange='owner', shard_sizes and CUDA tensors")
+        if not hasattr(ops, "contrastive_forward_block"):
+            raise ValueError("the peer transport needs the CUDA library's operators")
     return _ShardedContrastive.apply(queries, documents, doc_lengths, group, ops, exchange, shard_sizes,
-                                     records_group)
+                                     records_group, peer)
 
 
 def contrastive_targets(n_queries_local: int, *, group=None, device=None,

@@ -69,6 +69,26 @@ def _worker(rank, world, port, out_dir):
         torch.testing.assert_close(q.grad.float(), qf.grad[q0:q1].float(), rtol=2e-2, atol=2e-2)
         torch.testing.assert_close(d.grad.float(), df.grad[int(off[d0]):int(off[d1])].float(),
                                    rtol=2e-2, atol=2e-2)
+        # the owner exchange over peer-mapped buffers, two steps (the buffers alternate)
+        from maxsim_b200 import _ops
+        from maxsim_b200.peer import PeerExchange
+        lens_all = full["doc_lengths_all"].cpu()
+        sizes = []
+        for r in range(world):
+            a0, a1 = mdist.shard_range(n, r, world)
+            sizes.append((int(lens_all[a0:a1].sum()), a1 - a0, a1 - a0))
+        px = PeerExchange(max_doc_tokens=max(t for t, _, _ in sizes), max_docs=max(c for _, c, _ in sizes),
+                          max_queries=max(c for _, _, c in sizes), lq=q.shape[1], dim=q.shape[2],
+                          dtype=q.dtype)
+        for it in range(3):
+            q_p = part["queries"].clone().requires_grad_(True)
+            d_p = part["documents"].clone().requires_grad_(True)
+            s_p = mdist.score_contrastive_sharded(q_p, d_p, lens, shard_sizes=sizes, peer=px)
+            (s_p * g[q0:q1]).sum().backward()
+            assert torch.equal(s_p, s), f"peer transport, step {it}: scores differ"
+            assert torch.equal(q_p.grad, q.grad)
+            torch.testing.assert_close(d_p.grad.float(), d.grad.float(), rtol=2e-2, atol=2e-2)
+        assert _ops.device_status() == 0
         # rerank shard
         wl = W.c3_device_shard(rank * 3, rank * 3 + 3, dev, C=40)
         local = mdist.score_candidates_padded_sharded(wl["queries"], wl["documents"],
