@@ -377,6 +377,18 @@ MAXSIM_API int maxsim_b200_pack_owner_records_to(const int32_t* argmax, const fl
                                                  const int32_t* col_start,
                                                  int32_t* const* owner_blocks, int64_t n_owners,
                                                  int64_t Nq, int64_t Nb, int64_t Lq, void* stream);
+/* peer_gather copies n_segments small segments out of peer-mapped memory with
+ * one launch: table (device, n_segments rows of four int64: source address,
+ * destination selector 0 / 1, byte offset in that destination, bytes -- a
+ * multiple of 4); max_bytes is the largest segment (sizes the grid). */
+MAXSIM_API int maxsim_b200_peer_gather(const int64_t* table, int64_t n_segments, int64_t max_bytes,
+                                       void* dst0, void* dst1, void* stream);
+/* copy_many issues n device-to-device copies on `stream`, one asynchronous
+ * copy each (dst, src, bytes: HOST arrays of device addresses and sizes): the
+ * fetches of a step's shards out of peer-mapped memory through the copy
+ * engines at the cost of one call into the library. */
+MAXSIM_API int maxsim_b200_copy_many(void* const* dst, const void* const* src,
+                                     const int64_t* bytes, int64_t n, void* stream);
 MAXSIM_API int maxsim_b200_peer_barrier(uint32_t* const* flags, int64_t rank, int64_t world,
                                         uint32_t epoch, uint32_t polls, void* stream);
 

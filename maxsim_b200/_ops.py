@@ -68,6 +68,8 @@ _SIGNATURES = {
     "maxsim_contrastive_backward_documents_from_records": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, c_int, _P]),
     "maxsim_b200_pack_owner_records_to": (c_int, [_P] * 4 + [_I64] * 4 + [_P]),
     "maxsim_b200_peer_barrier": (c_int, [_P, _I64, _I64, ctypes.c_uint32, ctypes.c_uint32, _P]),
+    "maxsim_b200_peer_gather": (c_int, [_P, _I64, _I64, _P, _P, _P]),
+    "maxsim_b200_copy_many": (c_int, [_P, _P, _P, _I64, _P]),
     "maxsim_padded_backward_native": (c_int, [_P] * 8 + [_I64] * 5 + [c_int, _P]),
     "maxsim_contrastive_backward_native": (c_int, [_P] * 7 + [_I64] * 5 + [c_int, _P]),
 }
@@ -824,6 +826,37 @@ def pack_owner_records_to(argmax, dscore, col_start, owner_blocks) -> None:
             _ptr(a), _ptr(g), _ptr(cs), owner_blocks.data_ptr(), cs.shape[0] - 1, Nq, Nb, Lq,
             _stream_ptr())
     _check(rc, "maxsim_b200_pack_owner_records_to")
+
+
+def peer_gather(table, max_bytes: int, dst0, dst1=None) -> None:
+    """One launch that copies the segments listed in ``table`` (``[n, 4]`` int64
+    on the device: source address, destination 0 / 1, byte offset there, bytes)
+    out of peer-mapped memory into ``dst0`` / ``dst1``."""
+    dev = _require_cuda(table, dst0)
+    if table.dtype != torch.int64 or table.dim() != 2 or table.shape[1] != 4 or not table.is_contiguous():
+        raise ValueError("table must be a contiguous [n, 4] int64 tensor")
+    with _on_device(dev):
+        rc = load_library().maxsim_b200_peer_gather(
+            table.data_ptr(), table.shape[0], int(max_bytes), dst0.data_ptr(),
+            dst1.data_ptr() if dst1 is not None else None, _stream_ptr())
+    _check(rc, "maxsim_b200_peer_gather")
+
+
+def copy_many(dst_addresses, src_addresses, sizes, device) -> None:
+    """``len(sizes)`` asynchronous device-to-device copies on the current stream
+    of ``device`` (addresses and byte counts as Python ints) with one call
+    into the library."""
+    n = len(sizes)
+    if not (len(dst_addresses) == len(src_addresses) == n):
+        raise ValueError("dst_addresses, src_addresses and sizes must have one entry per copy")
+    if n == 0:
+        return
+    dst = (ctypes.c_void_p * n)(*dst_addresses)
+    src = (ctypes.c_void_p * n)(*src_addresses)
+    nbytes = (ctypes.c_int64 * n)(*sizes)
+    with _on_device(torch.device(device)):
+        rc = load_library().maxsim_b200_copy_many(dst, src, nbytes, n, _stream_ptr())
+    _check(rc, "maxsim_b200_copy_many")
 
 
 def peer_barrier(flags, rank: int, world: int, epoch: int, polls: int = 0) -> None:

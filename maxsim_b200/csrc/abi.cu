@@ -968,6 +968,38 @@ int maxsim_b200_pack_owner_records_to(const int32_t* argmax, const float* dscore
                                    owner_blocks, stream);
 }
 
+int maxsim_b200_peer_gather(const int64_t* table, int64_t n_segments, int64_t max_bytes, void* dst0,
+                            void* dst1, void* stream) {
+  if (n_segments < 0 || n_segments > 65535 || max_bytes < 0)
+    return fail(MAXSIM_EINVAL, "segment count out of range");
+  if (n_segments == 0 || max_bytes == 0) return MAXSIM_OK;
+  if (!table || !dst0) return fail(MAXSIM_EINVAL, "null pointer argument");
+  // enough CTAs per segment to keep a few loads in flight on every link, never more than the
+  // largest segment has 4 KB pieces
+  int64_t gx = (max_bytes + 4095) / 4096;
+  const int64_t cap = ((int64_t)sm_count() * 4 + n_segments - 1) / n_segments;
+  if (gx > cap) gx = cap;
+  if (gx < 1) gx = 1;
+  dim3 grid((unsigned)gx, (unsigned)n_segments);
+  peer_gather_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(table, dst0, dst1);
+  return launch_check("peer_gather_kernel");
+}
+
+int maxsim_b200_copy_many(void* const* dst, const void* const* src, const int64_t* bytes,
+                          int64_t n, void* stream) {
+  if (n < 0) return fail(MAXSIM_EINVAL, "negative count");
+  if (n == 0) return MAXSIM_OK;
+  if (!dst || !src || !bytes) return fail(MAXSIM_EINVAL, "null pointer argument");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  for (int64_t i = 0; i < n; ++i) {
+    if (bytes[i] < 0) return fail(MAXSIM_EINVAL, "negative size");
+    if (bytes[i] == 0) continue;
+    if (!dst[i] || !src[i]) return fail(MAXSIM_EINVAL, "null pointer argument");
+    MAXSIM_CUDA(cudaMemcpyAsync(dst[i], src[i], (size_t)bytes[i], cudaMemcpyDeviceToDevice, st));
+  }
+  return MAXSIM_OK;
+}
+
 int maxsim_b200_peer_barrier(uint32_t* const* flags, int64_t rank, int64_t world, uint32_t epoch,
                              uint32_t polls, void* stream) {
   if (world <= 0 || world > 1024 || rank < 0 || rank >= world)

@@ -1103,4 +1103,32 @@ __global__ void peer_barrier_kernel(uint32_t* const* __restrict__ flags, int ran
   }
 }
 
+// ---------------------------------------------------------------------------
+// Gather of small segments out of peer-mapped memory with plain loads: the
+// document lengths and the queries of all ranks in one launch each instead of
+// one copy per rank.  table[s] = {source address, which destination (0 / 1),
+// byte offset in it, bytes}; bytes are a multiple of 4, and 16-byte words are
+// used when source, destination and size allow.  blockIdx.y is the segment.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+peer_gather_kernel(const int64_t* __restrict__ table, void* __restrict__ dst0,
+                   void* __restrict__ dst1) {
+  const int64_t* row = table + 4 * (int64_t)blockIdx.y;
+  const char* src = reinterpret_cast<const char*>(row[0]);
+  char* dst = reinterpret_cast<char*>(row[1] ? dst1 : dst0) + row[2];
+  const int64_t bytes = row[3];
+  const int64_t first = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t step = (int64_t)gridDim.x * blockDim.x;
+  const bool wide = (((uintptr_t)src | (uintptr_t)dst | (uintptr_t)bytes) & 15) == 0;
+  if (wide) {
+    const int4* s4 = reinterpret_cast<const int4*>(src);
+    int4* d4 = reinterpret_cast<int4*>(dst);
+    for (int64_t w = first; w < bytes / 16; w += step) d4[w] = s4[w];
+  } else {
+    const int32_t* s1 = reinterpret_cast<const int32_t*>(src);
+    int32_t* d1 = reinterpret_cast<int32_t*>(dst);
+    for (int64_t w = first; w < bytes / 4; w += step) d1[w] = s1[w];
+  }
+}
+
 }  // namespace maxsim

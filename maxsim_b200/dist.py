@@ -39,6 +39,12 @@ Contrastive training
     ``opts = ProcessGroupNCCL.Options(is_high_priority_stream=True);
     opts.config.max_ctas = COLLECTIVE_SMS`` keeps its collectives within them.
 
+    ``peer=`` (a :class:`maxsim_b200.peer.PeerExchange`) replaces the
+    collectives by the node's peer-mapped memory: shards are fetched by the
+    copy engines out of the owners' buffers while forward launches keep every
+    SM, the regrouping kernel stores each owner's records into that owner's
+    memory, and one small barrier kernel per pass orders the two.
+
 Both drivers take the operator namespace as a parameter so that their
 sharding / reassembly logic can be exercised on CPU ``gloo`` ranks with a
 stand-in scorer; the default is the CUDA library, whose extra entry points
@@ -343,32 +349,30 @@ class _ShardedContrastive(torch.autograd.Function):
         docs_all = torch.empty((sum(tokens), d_local.shape[1]), dtype=d_local.dtype, device=dev)
         lens_all = torch.empty((col0[-1],), dtype=torch.int32, device=dev)
         q_all = torch.empty((sum(n_queries),) + tuple(q.shape[1:]), dtype=q.dtype, device=dev)
-        lens_event, doc_events, q_event, order = peer.gather(d_local, lens_local, q, sizes, docs_all,
-                                                             lens_all, q_all)
+        after_event, before_event, all_event = peer.gather(d_local, lens_local, q, sizes, docs_all,
+                                                           lens_all, q_all)
         main = torch.cuda.current_stream(dev)
         off_local = _offsets(ops, lens_local)
+        offsets = _offsets(ops, lens_all)
         scores = torch.empty((q.shape[0], col0[-1]), dtype=torch.float32, device=dev)
         argmax = torch.empty((q.shape[0], col0[-1], q.shape[1]), dtype=torch.int32, device=dev)
         blocks = ops.contrastive_forward_block(q, d_local, off_local, scores, argmax, col0[rank],
                                                tokens[rank])
-        main.wait_event(lens_event)
-        offsets = _offsets(ops, lens_all)
         if blocks:
             # the shards arrive in ring order: those after this rank's own, then those before
             # it.  Each of the two runs is a contiguous range of columns and gets one launch
             # (the copies are far quicker than the block scored meanwhile, and every launch
             # pays its own ramp-up and tail).
-            for first, last in ((rank + 1, world), (0, rank)):
+            for first, last, event in ((rank + 1, world, after_event), (0, rank, before_event)):
                 if col0[last] == col0[first]:
                     continue
-                main.wait_event(doc_events[last - 1])  # the copies complete in the order issued
+                main.wait_event(event)
                 ops.contrastive_forward_block(q, docs_all, offsets[col0[first]:col0[last] + 1], scores,
                                               argmax, col0[first], sum(tokens[first:last]))
+            main.wait_event(all_event)  # every read of a peer's buffers is ordered before what follows
         else:  # shape outside the block kernel: one ordinary call over all shards
-            for r in order:
-                main.wait_event(doc_events[r])
+            main.wait_event(all_event)
             scores, argmax = ops.maxsim_contrastive_forward_with_argmax(q, docs_all, offsets)
-        main.wait_event(q_event)  # every read of a peer's buffers is now ordered before what follows
         ctx.save_for_backward(q, docs_all, offsets, argmax, d_local, off_local)
         ctx.q_all, ctx.h_q = q_all, _Done()
         ctx.tokens, ctx.n_docs, ctx.n_queries, ctx.col0 = tokens, n_docs, n_queries, col0

@@ -30,7 +30,7 @@ is set before the first allocation unless the caller has set it).
 from __future__ import annotations
 
 import os
-from typing import List, Sequence, Tuple
+from typing import Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -132,15 +132,19 @@ class PeerExchange:
     # -- forward -------------------------------------------------------------
 
     def gather(self, documents, lengths, queries, sizes, docs_all, lens_all, q_all):
-        """Publish this rank's shard and start fetching all others into the
+        """Publish this rank's shard and gather all shards into the
         rank-ordered ``docs_all [T_total, D]``, ``lens_all [Nb_total]`` and
-        ``q_all [Nq_total, Lq, D]``.  Returns ``(lens_event, doc_events, q_event,
-        order)``: ``lens_event`` fires when all lengths are there,
-        ``doc_events[r]`` when rank r's documents have landed, ``q_event`` when
-        everything has (all queries and this rank's own rows of ``docs_all``
-        included); ``order`` lists the other ranks in the order their documents
-        are fetched.  The caller's tensors must stay untouched until
-        ``q_event`` has been waited for."""
+        ``q_all [Nq_total, Lq, D]``.
+
+        The lengths are complete on the current stream when this returns (one
+        small kernel reads them out of the peers' buffers).  The documents
+        travel as one copy-engine copy per owner on a side stream (the ranks
+        after this one, then those before it); the queries and this rank's own
+        rows follow on a second side stream.  Each group of copies is issued by
+        one call into the library.  Returns
+        ``(after_event, before_event, all_event)``: the documents of the ranks
+        after / before this one have landed; everything has.  The caller's
+        tensors must stay untouched until ``all_event`` has been waited for."""
         rank, world = self.rank, self.world
         tokens = [s[0] for s in sizes]
         n_docs = [s[1] for s in sizes]
@@ -148,45 +152,84 @@ class PeerExchange:
         slot = self._fwd_steps & 1
         self._fwd_steps += 1
         main = torch.cuda.current_stream(self.device)
+        plan = self._plan(slot, tuple(tokens), tuple(n_docs), tuple(n_queries))
 
-        self._view(rank, self._docs_at[slot], (tokens[rank], self.dim), self.dtype).copy_(documents)
-        self._view(rank, self._lens_at[slot], (n_docs[rank],), torch.int32).copy_(lengths)
-        self._view(rank, self._q_at[slot], (n_queries[rank], self.lq, self.dim), self.dtype).copy_(queries)
+        item = self._item
+        dev = self.device
+        if not (documents.is_contiguous() and lengths.is_contiguous() and queries.is_contiguous()):
+            raise ValueError("the peer transport takes contiguous tensors")
+        # publish: this rank's rows into its own peer-visible buffer
+        _ops.copy_many(plan["own_dst"], [documents.data_ptr(), lengths.data_ptr(), queries.data_ptr()],
+                       plan["own_bytes"], dev)
         self.barrier()
-        ready = torch.cuda.Event()
+        ready = plan["events"][0]
         ready.record(main)
+        _ops.peer_gather(plan["lens_table"], plan["lens_max"], lens_all)
 
-        d_views = list(docs_all.split(tokens, dim=0))
-        l_views = list(lens_all.split(n_docs, dim=0))
-        q_views = list(q_all.split(n_queries, dim=0))
-
-        order = [(rank + k) % world for k in range(1, world)]
-        with torch.cuda.stream(self._fetch_small):
-            self._fetch_small.wait_event(ready)
-            l_views[rank].copy_(lengths)
-            for r in order:
-                if n_docs[r]:
-                    l_views[r].copy_(self._view(r, self._lens_at[slot], (n_docs[r],), torch.int32))
-            lens_event = torch.cuda.Event()
-            lens_event.record(self._fetch_small)
-            for r in order:
-                if n_queries[r]:
-                    q_views[r].copy_(self._view(r, self._q_at[slot], (n_queries[r], self.lq, self.dim), self.dtype))
-            # this rank's own pieces: needed by the backward pass only
-            q_views[rank].copy_(queries)
-            d_views[rank].copy_(documents)
-            q_event = torch.cuda.Event()
-            q_event.record(self._fetch_small)
-        doc_events: List[torch.cuda.Event] = [None] * world
+        row_bytes = self.dim * item
+        d_base, q_base = docs_all.data_ptr(), q_all.data_ptr()
+        row, q0 = plan["row0"], plan["q0"]
+        q_bytes = self.lq * row_bytes
         with torch.cuda.stream(self._fetch_docs):
             self._fetch_docs.wait_event(ready)
-            for r in order:
-                if tokens[r]:
-                    d_views[r].copy_(self._view(r, self._docs_at[slot], (tokens[r], self.dim), self.dtype))
-                ev = torch.cuda.Event()
-                ev.record(self._fetch_docs)
-                doc_events[r] = ev
-        return lens_event, doc_events, q_event, order
+            after = range(rank + 1, world)
+            _ops.copy_many([d_base + row[r] * row_bytes for r in after],
+                           [plan["docs_src"][r] for r in after],
+                           [tokens[r] * row_bytes for r in after], dev)
+            after_event = plan["events"][1]
+            after_event.record(self._fetch_docs)
+            before = range(0, rank)
+            _ops.copy_many([d_base + row[r] * row_bytes for r in before],
+                           [plan["docs_src"][r] for r in before],
+                           [tokens[r] * row_bytes for r in before], dev)
+            before_event = plan["events"][2]
+            before_event.record(self._fetch_docs)
+        with torch.cuda.stream(self._fetch_small):
+            self._fetch_small.wait_event(ready)
+            # needed by the backward pass only: all queries, this rank's own document rows
+            others = [r for r in range(world) if r != rank]
+            _ops.copy_many(
+                [q_base + q0[r] * q_bytes for r in others] + [q_base + q0[rank] * q_bytes,
+                                                             d_base + row[rank] * row_bytes],
+                [plan["q_src"][r] for r in others] + [queries.data_ptr(), documents.data_ptr()],
+                [n_queries[r] * q_bytes for r in others] + [n_queries[rank] * q_bytes,
+                                                            tokens[rank] * row_bytes], dev)
+            self._fetch_small.wait_event(before_event)
+            all_event = plan["events"][3]
+            all_event.record(self._fetch_small)
+        return after_event, before_event, all_event
+
+    def _plan(self, slot, tokens, n_docs, n_queries):
+        """Views, tables and events of one (slot, shard sizes) combination;
+        built once, a training loop asks for the same two every step."""
+        key = ("fwd", slot, tokens, n_docs, n_queries)
+        plan = self._tables.get(key)
+        if plan is not None:
+            return plan
+        if len(self._tables) > 64:
+            self._tables.clear()
+        rank, world = self.rank, self.world
+        item = self._item
+        row0 = [sum(tokens[:r]) for r in range(world + 1)]
+        doc0 = [sum(n_docs[:r]) for r in range(world + 1)]
+        q0 = [sum(n_queries[:r]) for r in range(world + 1)]
+        q_bytes = self.lq * self.dim * item
+        lens_rows = [[self._bases[r] + self._lens_at[slot], 0, 4 * doc0[r], 4 * n_docs[r]]
+                     for r in range(world) if n_docs[r]]
+        plan = {
+            "own_dst": [self._bases[rank] + self._docs_at[slot], self._bases[rank] + self._lens_at[slot],
+                        self._bases[rank] + self._q_at[slot]],
+            "own_bytes": [tokens[rank] * self.dim * item, 4 * n_docs[rank], n_queries[rank] * q_bytes],
+            "docs_src": [self._bases[r] + self._docs_at[slot] for r in range(world)],
+            "q_src": [self._bases[r] + self._q_at[slot] for r in range(world)],
+            "row0": row0,
+            "q0": q0,
+            "lens_table": torch.tensor(lens_rows, dtype=torch.int64, device=self.device).reshape(len(lens_rows), 4),
+            "lens_max": max([4 * n for n in n_docs] + [0]),
+            "events": [torch.cuda.Event() for _ in range(4)],
+        }
+        self._tables[key] = plan
+        return plan
 
     # -- backward ------------------------------------------------------------
 

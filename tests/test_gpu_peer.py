@@ -64,3 +64,43 @@ def test_barrier_passes_when_the_peers_have_signalled_and_reports_when_they_have
     # a single rank has nobody to wait for
     _ops.peer_barrier(table, 0, 1, 5)
     assert _ops.device_status() == 0
+
+
+def test_gather_of_segments_by_address():
+    from maxsim_b200 import _ops
+    dev = _dev()
+    gen = torch.Generator().manual_seed(5)
+    srcs = [torch.randint(-1000, 1000, (n,), generator=gen, dtype=torch.int32).to(dev)
+            for n in (7, 1024, 36, 4096 + 4)]
+    dst0 = torch.full((8000,), -1, dtype=torch.int32, device=dev)
+    dst1 = torch.full((6000,), -1, dtype=torch.int32, device=dev)
+    # (source, destination, offset in words): aligned and unaligned pieces, both destinations
+    plan = [(0, 0, 3), (1, 1, 16), (2, 0, 100), (3, 1, 1200)]
+    rows = [[srcs[i].data_ptr(), which, 4 * at, 4 * srcs[i].numel()] for i, which, at in plan]
+    table = torch.tensor(rows, dtype=torch.int64, device=dev)
+    _ops.peer_gather(table, max(r[3] for r in rows), dst0, dst1)
+    want0 = torch.full((8000,), -1, dtype=torch.int32, device=dev)
+    want1 = torch.full((6000,), -1, dtype=torch.int32, device=dev)
+    for i, which, at in plan:
+        (want1 if which else want0)[at:at + srcs[i].numel()] = srcs[i]
+    assert torch.equal(dst0, want0) and torch.equal(dst1, want1)
+    # nothing to do
+    _ops.peer_gather(table[:0].contiguous(), 0, dst0)
+
+
+def test_many_copies_with_one_call():
+    from maxsim_b200 import _ops
+    dev = _dev()
+    gen = torch.Generator().manual_seed(9)
+    srcs = [torch.randint(0, 255, (n,), generator=gen, dtype=torch.uint8).to(dev) for n in (5, 4096, 0, 333)]
+    dst = torch.zeros(6000, dtype=torch.uint8, device=dev)
+    at = [10, 100, 4500, 5000]
+    _ops.copy_many([dst.data_ptr() + a for a in at], [s.data_ptr() for s in srcs],
+                   [s.numel() for s in srcs], dev)
+    want = torch.zeros(6000, dtype=torch.uint8, device=dev)
+    for a, s in zip(at, srcs):
+        want[a:a + s.numel()] = s
+    assert torch.equal(dst, want)
+    _ops.copy_many([], [], [], dev)
+    with pytest.raises(ValueError):
+        _ops.copy_many([1], [], [4], dev)
