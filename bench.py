@@ -654,7 +654,8 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
         peer = PeerExchange(max_doc_tokens=max(s[0] for s in shard_sizes),
                             max_docs=max(s[1] for s in shard_sizes),
                             max_queries=max(s[2] for s in shard_sizes),
-                            lq=q.shape[1], dim=q.shape[2], dtype=q.dtype)
+                            lq=q.shape[1], dim=q.shape[2], dtype=q.dtype,
+                            wait_polls=1 << 21)  # a barrier gives up after about two seconds
     except Exception as exc:  # noqa: BLE001 -- reported in the record
         peer_error = f"{type(exc).__name__}: {exc}"[:300]
     have = torch.tensor([1 if peer is not None else 0], device=dev)
@@ -737,7 +738,55 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
     ms_owner = timed("owner")
     ms_nccl = timed("owner", shard_sizes)
     ms_peer = timed("owner", shard_sizes, peer) if peer is not None else None
-    ms = ms_peer if ms_peer is not None else ms_nccl
+
+    # the same step over the peer transport, captured in CUDA graphs and replayed
+    ms_graph, graph_error, par_graph = None, None, None
+    if peer is not None:
+        stepper = None
+        try:
+            stepper = maxsim.GraphedShardedContrastiveStep(peer, shard_sizes)
+        except Exception as exc:  # noqa: BLE001 -- reported in the record
+            graph_error = f"{type(exc).__name__}: {exc}"[:300]
+        have = torch.tensor([1 if stepper is not None else 0], device=dev)
+        dist.all_reduce(have, op=dist.ReduceOp.MIN)
+        if bool(have.item()):
+            qd, dd_ = q.detach(), d.detach()
+            loss_g, gq, gd = stepper.step(qd, dd_, lens)
+            loss_all = loss_g.detach().double().clone()
+            dist.all_reduce(loss_all)
+            ref_loss = float(torch.nn.functional.cross_entropy(s_full.detach(), tf))
+            dq_err = float((gq.float() - qf.grad[q0:q1].float()).abs().max())
+            dd_err = float((gd.float() - df.grad[t0:t1].float()).abs().max())
+            status = torch.tensor([_ops_status()], device=dev)
+            dist.all_reduce(status, op=dist.ReduceOp.MAX)
+            ok = (abs(float(loss_all) - ref_loss) <= 1e-4 * max(1.0, abs(ref_loss))
+                  and dq_err <= 1e-2 * max(1e-6, float(qf.grad.float().abs().max()))
+                  and dd_err <= 2e-2 * max(1e-6, float(df.grad[t0:t1].float().abs().max()))
+                  and int(status.item()) == 0)
+            flag = torch.tensor([1 if ok else 0], device=dev)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            par_graph = {"loss": float(loss_all), "loss_single_gpu": ref_loss,
+                         "grad_q_max_abs_diff_vs_single_gpu": dq_err,
+                         "grad_d_max_abs_diff_vs_single_gpu": dd_err,
+                         "device_status_all_ranks": int(status.item()),
+                         "ok_all_ranks": bool(flag.item())}
+            parity_ok = parity_ok and par_graph["ok_all_ranks"]
+            if par_graph["ok_all_ranks"]:
+                for _ in range(4):
+                    stepper.step(qd, dd_, lens)
+                torch.cuda.synchronize()
+                dist.barrier()
+                iters = 10
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(iters):
+                    stepper.step(qd, dd_, lens)
+                e1.record()
+                torch.cuda.synchronize()
+                ms_graph = reduce_max(e0.elapsed_time(e1) / iters)
+        elif graph_error is None:
+            graph_error = "capture failed on another rank"
+    ms = ms_graph if ms_graph is not None else ms_peer if ms_peer is not None else ms_nccl
     T = int(full["doc_lengths_all"].sum().item())
     flops = 2 * 128 * n * 32 * T + 4 * 128 * n * n * 32
     return {"c5_contrastive_train_bf16_sharded": {
@@ -746,9 +795,14 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
         "efficiency": ms_single / ms / world,
         "tensor_frac_all_gpus": flops / (ms * 1e-3) / (world * peaks["bf16_tflops"] * 1e12),
         "parity_ok": parity_ok,
-        "transport": "peer" if ms_peer is not None else "nccl",
+        "transport": ("peer, step replayed from CUDA graphs" if ms_graph is not None
+                      else "peer" if ms_peer is not None else "nccl"),
         "peer_transport_unavailable": peer_error,
+        "graph_capture_unavailable": graph_error,
+        "ms_per_step_peer_eager": ms_peer,
+        "efficiency_peer_eager": (ms_single / ms_peer / world) if ms_peer is not None else None,
         "parity": {"owner": par_owner, "reduce_scatter": par_rs, "owner_peer_transport": par_peer,
+                   "owner_peer_transport_graphed": par_graph,
                    "owner_and_reduce_scatter_scores_equal": bool(same.item())},
         "ms_per_step_nccl": ms_nccl, "efficiency_nccl": ms_single / ms_nccl / world,
         "ms_per_step_sizes_exchanged_in_step": ms_owner,
@@ -759,6 +813,10 @@ def bench_sharded_train_step(dev, dist, rank, world, peaks, small=False):
                 "never waits for the device, over the transport named in 'transport' -- 'peer': "
                 "shards fetched from peer-mapped buffers by the copy engines, argmax records stored "
                 "into the owners' memory by the regrouping kernel, one barrier kernel per pass; "
+                "'peer, step replayed from CUDA graphs': the same, the whole step (input copies into "
+                "static buffers, exchange, forward, loss, both gradients) captured once per buffer "
+                "slot and replayed (GraphedShardedContrastiveStep), ms_per_step_peer_eager being the "
+                "eager form; "
                 "'nccl' (always measured, ms_per_step_nccl): per-owner broadcasts and an all-to-all; "
                 "ms_per_step_sizes_exchanged_in_step (nccl): the sizes "
                 "all-gathered and read back inside the step; ms_per_step_reduce_scatter: fp32 "
@@ -1124,7 +1182,8 @@ def run_gpu_arm(args):
                 short = {}
                 for key in ("ms_per_step", "forward_ms", "tensor_frac", "forward_tensor_frac",
                             "forward_unique_doc_hbm_frac", "step_hbm_frac", "single_gpu_ms_same_run",
-                            "efficiency", "transport", "ms_per_step_nccl", "efficiency_nccl",
+                            "efficiency", "transport", "ms_per_step_peer_eager", "efficiency_peer_eager",
+                            "ms_per_step_nccl", "efficiency_nccl",
                             "efficiency_reduce_scatter", "ms_per_step_reduce_scatter",
                             "parity_ok", "ms"):
                     if key in rec:

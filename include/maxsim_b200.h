@@ -368,11 +368,13 @@ MAXSIM_API int maxsim_contrastive_backward_documents_from_records(
  * belong): the kernel's stores are the transfer.
  * peer_barrier is the stream-ordered barrier that follows: flags (device
  * array of `world` pointers, flags[r] = rank r's `world` flag words, zero
- * before the first barrier) and an epoch that the caller raises by one per
- * barrier, the same on all ranks.  Stores made on `stream` before the barrier
- * are visible to a rank's kernels launched after its own barrier.  A rank
- * waits at most `polls` polls (0: about ten seconds) for each peer; a wait
- * that runs out sets bit 4 of the word maxsim_b200_device_status reports. */
+ * before the first barrier) and `counter`, one device word of this rank, zero
+ * before the first barrier, in which the kernel counts the barriers passed
+ * (every rank must pass the same sequence of barriers; a barrier captured in a
+ * CUDA graph keeps counting at every replay).  Stores made on `stream` before
+ * the barrier are visible to a rank's kernels launched after its own barrier.
+ * A rank waits at most `polls` polls (0: about ten seconds) for each peer; a
+ * wait that runs out sets bit 4 of the word maxsim_b200_device_status reports. */
 MAXSIM_API int maxsim_b200_pack_owner_records_to(const int32_t* argmax, const float* dscore,
                                                  const int32_t* col_start,
                                                  int32_t* const* owner_blocks, int64_t n_owners,
@@ -390,7 +392,7 @@ MAXSIM_API int maxsim_b200_peer_gather(const int64_t* table, int64_t n_segments,
 MAXSIM_API int maxsim_b200_copy_many(void* const* dst, const void* const* src,
                                      const int64_t* bytes, int64_t n, void* stream);
 MAXSIM_API int maxsim_b200_peer_barrier(uint32_t* const* flags, int64_t rank, int64_t world,
-                                        uint32_t epoch, uint32_t polls, void* stream);
+                                        uint32_t* counter, uint32_t polls, void* stream);
 
 /* Replaces maxsim_contrastive_backward (maxsim_cuda/maxsim.cu:1856-1920).
  * dscore [Nq, Nb]; grad_queries [Nq, Lq, dim], grad_documents

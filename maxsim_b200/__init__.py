@@ -28,7 +28,7 @@ import torch
 from . import _ops
 from . import _validate as _v
 from ._ops import device_status, ops
-from .graphed import GraphedContrastiveStep
+from .graphed import GraphedContrastiveStep, GraphedShardedContrastiveStep
 from .layout import (pack_padded, rerank_order, rerank_topk, score_candidates_padded_from_host,
                      unpack_packed)
 
@@ -41,7 +41,7 @@ __all__ = [
     "score_packed", "score_packed_with_argmax", "score_packed_train",
     "lengths_from_prefix_mask", "contrastive_loss",
     "pack_padded", "unpack_packed", "rerank_topk", "rerank_order",
-    "score_candidates_padded_from_host", "GraphedContrastiveStep", "device_status",
+    "score_candidates_padded_from_host", "GraphedContrastiveStep", "GraphedShardedContrastiveStep", "device_status",
 ]
 
 __version__ = "0.1.0"

@@ -67,7 +67,7 @@ _SIGNATURES = {
     "maxsim_b200_pack_owner_records": (c_int, [_P] * 3 + [_I64] * 4 + [_P, _P]),
     "maxsim_contrastive_backward_documents_from_records": (c_int, [_P] * 5 + [_I64] * 5 + [c_int, c_int, _P]),
     "maxsim_b200_pack_owner_records_to": (c_int, [_P] * 4 + [_I64] * 4 + [_P]),
-    "maxsim_b200_peer_barrier": (c_int, [_P, _I64, _I64, ctypes.c_uint32, ctypes.c_uint32, _P]),
+    "maxsim_b200_peer_barrier": (c_int, [_P, _I64, _I64, _P, ctypes.c_uint32, _P]),
     "maxsim_b200_peer_gather": (c_int, [_P, _I64, _I64, _P, _P, _P]),
     "maxsim_b200_copy_many": (c_int, [_P, _P, _P, _I64, _P]),
     "maxsim_padded_backward_native": (c_int, [_P] * 8 + [_I64] * 5 + [c_int, _P]),
@@ -859,14 +859,17 @@ def copy_many(dst_addresses, src_addresses, sizes, device) -> None:
     _check(rc, "maxsim_b200_copy_many")
 
 
-def peer_barrier(flags, rank: int, world: int, epoch: int, polls: int = 0) -> None:
+def peer_barrier(flags, rank: int, world: int, counter, polls: int = 0) -> None:
     """Stream-ordered barrier between the ranks of a node over flag words in
     peer-mapped memory (``flags``: ``[world]`` int64 addresses on the device,
-    see the header); ``epoch`` grows by one per barrier on every rank."""
-    dev = _require_cuda(flags)
+    see the header); ``counter`` is this rank's one-word int32 tensor in which
+    the kernel counts the barriers passed."""
+    dev = _require_cuda(flags, counter)
+    if counter.dtype != torch.int32 or counter.numel() != 1:
+        raise ValueError("counter must be a one-element int32 tensor")
     with _on_device(dev):
         rc = load_library().maxsim_b200_peer_barrier(
-            flags.data_ptr(), int(rank), int(world), int(epoch) & 0xFFFFFFFF, int(polls), _stream_ptr())
+            flags.data_ptr(), int(rank), int(world), counter.data_ptr(), int(polls), _stream_ptr())
     _check(rc, "maxsim_b200_peer_barrier")
 
 

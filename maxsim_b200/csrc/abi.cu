@@ -1000,15 +1000,14 @@ int maxsim_b200_copy_many(void* const* dst, const void* const* src, const int64_
   return MAXSIM_OK;
 }
 
-int maxsim_b200_peer_barrier(uint32_t* const* flags, int64_t rank, int64_t world, uint32_t epoch,
-                             uint32_t polls, void* stream) {
+int maxsim_b200_peer_barrier(uint32_t* const* flags, int64_t rank, int64_t world,
+                             uint32_t* counter, uint32_t polls, void* stream) {
   if (world <= 0 || world > 1024 || rank < 0 || rank >= world)
     return fail(MAXSIM_EINVAL, "rank / world out of range");
-  if (world == 1) return MAXSIM_OK;
-  if (!flags) return fail(MAXSIM_EINVAL, "null pointer argument");
+  if (!flags || !counter) return fail(MAXSIM_EINVAL, "null pointer argument");
   const unsigned threads = (unsigned)((world + 31) / 32 * 32);
   peer_barrier_kernel<<<1, threads, 0, static_cast<cudaStream_t>(stream)>>>(
-      flags, (int)rank, (int)world, epoch, polls ? polls : (1u << 24));
+      flags, (int)rank, (int)world, counter, polls ? polls : (1u << 24));
   return launch_check("peer_barrier_kernel");
 }
 

@@ -1076,16 +1076,22 @@ pack_owner_records_kernel(const int32_t* __restrict__ argmax, const float* __res
 // ---------------------------------------------------------------------------
 // Barrier between the ranks of one node over flags in peer-mapped memory.
 // flags[r] points at rank r's flag words (one per rank) as mapped into this
-// process; thread t tells rank t that this rank has reached barrier `epoch`
+// process; thread t tells rank t that this rank has reached its next barrier
 // (a release store at system scope into flags[t][rank], after the stream's
 // earlier stores to peer memory) and waits until rank t has said the same
 // (flags[rank][t] >= epoch; epochs only grow, so a peer that is already one
-// barrier ahead satisfies the wait too).  The wait is bounded: after `limit`
-// polls the kernel sets bit 4 of the status word and returns.
+// barrier ahead satisfies the wait too).  The epoch is the number of barriers
+// this rank has passed plus one, kept in `counter` on the device -- not a
+// launch argument, so that a barrier captured in a CUDA graph counts on at
+// every replay.  The wait is bounded: after `limit` polls the kernel sets bit 4
+// of the status word and returns.
 // ---------------------------------------------------------------------------
 __global__ void peer_barrier_kernel(uint32_t* const* __restrict__ flags, int rank, int world,
-                                    uint32_t epoch, uint32_t limit) {
+                                    uint32_t* __restrict__ counter, uint32_t limit) {
   const int t = threadIdx.x;
+  const uint32_t epoch = *counter + 1;
+  __syncthreads();  // every thread has read the old count
+  if (t == 0) *counter = epoch;
   if (t >= world || t == rank) return;
   __threadfence_system();
   uint32_t* theirs = flags[t] + rank;

@@ -20,7 +20,7 @@ from typing import Optional, Tuple
 
 import torch
 
-__all__ = ["GraphedContrastiveStep"]
+__all__ = ["GraphedContrastiveStep", "GraphedShardedContrastiveStep"]
 
 
 class GraphedContrastiveStep:
@@ -100,3 +100,95 @@ class GraphedContrastiveStep:
                 self._targets.copy_(targets, non_blocking=True)
         self._graph.replay()
         return self._loss, self._gq, self._gd[:T]
+
+
+class GraphedShardedContrastiveStep:
+    """The sharded contrastive train step (``maxsim_b200.dist``) over
+    peer-mapped buffers, captured in CUDA graphs and replayed.
+
+    With the problem split over the GPUs of a node each rank's share of a step
+    is a few hundred microseconds of kernels, the same order as the Python,
+    autograd and launch work that enqueues it; the slowest host then sets the
+    pace of all ranks (they meet at two barriers per step).  The peer transport
+    consists of kernels, copies and events only, so the whole step -- publish,
+    barrier, fetches on the side streams, forward launches, loss, record
+    stores, barrier, both gradients -- can be captured and replayed with one
+    host call.  The barrier counts its epochs on the device, and the exchange
+    buffers alternate between two slots, so two graphs are captured (one per
+    slot) and replayed in turn.
+
+    Every rank builds the object with the same ``shard_sizes`` (list of every
+    rank's ``(document tokens, documents, queries)``), which are fixed for its
+    lifetime (batches packed to a fixed token count per rank; a rank with fewer
+    tokens pads its last document).  ``step(queries, documents, doc_lengths)``
+    copies this rank's shard into static buffers, replays, and returns ``(loss,
+    grad_queries, grad_documents)``: this rank's part of the global mean
+    cross-entropy of ``scores / temperature`` against in-batch targets (query i
+    of rank r is paired with document i of rank r) and the gradients of the
+    global loss with respect to this rank's shard.  The returned tensors are
+    static buffers, overwritten two steps later.  All ranks must call ``step``
+    the same number of times.
+    """
+
+    def __init__(self, peer, shard_sizes, *, temperature: float = 1.0):
+        from . import dist as mdist
+
+        if not temperature > 0:
+            raise ValueError(f"temperature must be > 0; got {temperature}")
+        self.peer = peer
+        self.sizes = [(int(t), int(n), int(nq)) for t, n, nq in shard_sizes]
+        peer.check_fits(self.sizes, peer.lq, peer.dim, peer.dtype)
+        rank, dev = peer.rank, peer.device
+        tokens, n_docs, n_queries = self.sizes[rank]
+        self.temperature = float(temperature)
+        n_total = sum(s[2] for s in self.sizes)
+        self._q = torch.zeros((n_queries, peer.lq, peer.dim), dtype=peer.dtype, device=dev, requires_grad=True)
+        self._d = torch.zeros((tokens, peer.dim), dtype=peer.dtype, device=dev, requires_grad=True)
+        # one token per document and the rest in the last one: valid lengths until the first step
+        lens = [1] * n_docs
+        lens[-1] = tokens - (n_docs - 1)
+        self._lens = torch.tensor(lens, dtype=torch.int32, device=dev)
+        self._targets = mdist.contrastive_targets(n_queries, group=peer.group, device=dev,
+                                                  docs_per_rank=[s[1] for s in self.sizes])
+
+        def body():
+            scores = mdist.score_contrastive_sharded(self._q, self._d, self._lens, group=peer.group,
+                                                     shard_sizes=self.sizes, peer=peer)
+            loss = torch.nn.functional.cross_entropy(scores / self.temperature, self._targets,
+                                                     reduction="sum") / n_total
+            gq, gd = torch.autograd.grad(loss, (self._q, self._d))
+            return loss, gq, gd
+
+        # Warm up on a side stream: an even number of steps, so that the capture of the first
+        # graph meets slot 0 again, and every table the step needs exists before capture.
+        with torch.cuda.device(dev):
+            side = torch.cuda.Stream(device=dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    body()
+            torch.cuda.current_stream(dev).wait_stream(side)
+            self._graphs, self._outs = [], []
+            for _ in range(2):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    out = body()
+                self._graphs.append(graph)
+                self._outs.append(out)
+        self._k = 0
+
+    def step(self, queries: torch.Tensor, documents: torch.Tensor, doc_lengths: torch.Tensor
+             ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        if tuple(queries.shape) != tuple(self._q.shape) or tuple(documents.shape) != tuple(self._d.shape):
+            raise ValueError(f"this rank's shard must be queries {tuple(self._q.shape)} and documents "
+                             f"{tuple(self._d.shape)}; got {tuple(queries.shape)} and {tuple(documents.shape)}")
+        if doc_lengths.numel() != self._lens.numel():
+            raise ValueError(f"doc_lengths must have {self._lens.numel()} elements")
+        with torch.no_grad():
+            self._q.copy_(queries, non_blocking=True)
+            self._d.copy_(documents, non_blocking=True)
+            self._lens.copy_(doc_lengths, non_blocking=True)
+        k = self._k & 1
+        self._k += 1
+        self._graphs[k].replay()
+        return self._outs[k]

@@ -100,7 +100,7 @@ class PeerExchange:
             self._flags = torch.tensor([b + self._flags_at for b in bases], dtype=torch.int64, device=self.device)
             self._fetch_small = torch.cuda.Stream(self.device)
             self._fetch_docs = torch.cuda.Stream(self.device)
-        self._epoch = 0
+        self._counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._fwd_steps = 0
         self._bwd_steps = 0
         self._tables = {}
@@ -126,8 +126,7 @@ class PeerExchange:
 
     def barrier(self) -> None:
         """Stream-ordered barrier of the group on the current stream."""
-        self._epoch += 1
-        _ops.peer_barrier(self._flags, self.rank, self.world, self._epoch, self.wait_polls)
+        _ops.peer_barrier(self._flags, self.rank, self.world, self._counter, self.wait_polls)
 
     # -- forward -------------------------------------------------------------
 

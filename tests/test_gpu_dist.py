@@ -89,6 +89,22 @@ def _worker(rank, world, port, out_dir):
             assert torch.equal(q_p.grad, q.grad)
             torch.testing.assert_close(d_p.grad.float(), d.grad.float(), rtol=2e-2, atol=2e-2)
         assert _ops.device_status() == 0
+        # the same step replayed from CUDA graphs (one per buffer slot), on changing inputs
+        stepper = maxsim.GraphedShardedContrastiveStep(px, sizes)
+        target = mdist.contrastive_targets(q1 - q0, device=dev, docs_per_rank=[c for _, c, _ in sizes])
+        for it in range(4):
+            q_in = (part["queries"].float() * (1.0 + 0.25 * it)).to(part["queries"].dtype)
+            d_in = part["documents"].roll(it, 0).contiguous()
+            loss_g, gq, gd = stepper.step(q_in, d_in, lens)
+            q_e = q_in.clone().requires_grad_(True)
+            d_e = d_in.clone().requires_grad_(True)
+            s_e = mdist.score_contrastive_sharded(q_e, d_e, lens, shard_sizes=sizes, peer=px)
+            loss_e = torch.nn.functional.cross_entropy(s_e, target, reduction="sum") / n
+            loss_e.backward()
+            torch.testing.assert_close(loss_g, loss_e.detach(), rtol=1e-5, atol=1e-6)
+            assert torch.equal(gq, q_e.grad), f"graphed step {it}: grad_queries differ"
+            torch.testing.assert_close(gd.float(), d_e.grad.float(), rtol=2e-2, atol=1e-6)
+        assert _ops.device_status() == 0
         # rerank shard
         wl = W.c3_device_shard(rank * 3, rank * 3 + 3, dev, C=40)
         local = mdist.score_candidates_padded_sharded(wl["queries"], wl["documents"],

@@ -50,20 +50,22 @@ def test_barrier_passes_when_the_peers_have_signalled_and_reports_when_they_have
     world, rank = 4, 1
     flags = [torch.zeros(world, dtype=torch.int32, device=dev) for _ in range(world)]
     table = torch.tensor([f.data_ptr() for f in flags], dtype=torch.int64, device=dev)
-    # the peers are already at epoch 1 (one of them a barrier ahead)
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
+    # the peers are already at barrier 1 (one of them a barrier ahead)
     flags[rank].copy_(torch.tensor([1, 0, 2, 1], dtype=torch.int32))
-    _ops.peer_barrier(table, rank, world, 1, polls=2000)
-    assert _ops.device_status() == 0
+    _ops.peer_barrier(table, rank, world, counter, polls=2000)
+    assert _ops.device_status() == 0 and int(counter.item()) == 1
     for r in range(world):
         if r != rank:
             assert flags[r].tolist()[rank] == 1  # this rank's arrival, stored in every peer's flags
-    # epoch 2: rank 2 is there, ranks 0 and 3 never arrive -- the wait gives up and says so
-    _ops.peer_barrier(table, rank, world, 2, polls=2000)
+    # barrier 2: rank 2 is there, ranks 0 and 3 never arrive -- the wait gives up and says so
+    _ops.peer_barrier(table, rank, world, counter, polls=2000)
     assert _ops.device_status() & 4
-    assert _ops.device_status() == 0
+    assert _ops.device_status() == 0 and int(counter.item()) == 2
     # a single rank has nobody to wait for
-    _ops.peer_barrier(table, 0, 1, 5)
-    assert _ops.device_status() == 0
+    alone = torch.zeros(1, dtype=torch.int32, device=dev)
+    _ops.peer_barrier(table, 0, 1, alone)
+    assert _ops.device_status() == 0 and int(alone.item()) == 1
 
 
 def test_gather_of_segments_by_address():
