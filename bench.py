@@ -1198,6 +1198,86 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
+def run_sharded_timeline(args):
+    """Launched under torchrun on N GPUs: a few sharded contrastive train steps
+    of the ties configuration under the torch profiler; rank 0 prints the
+    device timeline of the last step (start and duration of every kernel and
+    copy, microseconds) and every rank how long its barriers waited.  Not a
+    bench value: the profiler slows the host side."""
+    import torch.distributed as dist
+    from torch.profiler import ProfilerActivity, profile
+
+    from maxsim_b200 import dist as mdist
+    from maxsim_b200 import workloads as W
+
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world < 2:
+        raise SystemExit("--timeline-sharded needs torchrun with at least two ranks")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+    opts.config.max_ctas = mdist.COLLECTIVE_SMS
+    opts.config.cga_cluster_size = 1
+    dist.init_process_group("nccl", device_id=dev, pg_options=opts)
+    n = 256 if args.small else 1024
+    full = W.c5_device(dev, Nq=n, Nb=n)
+    off = full["document_offsets"].cpu()
+    lens_host = full["doc_lengths_all"].cpu()
+    q0, q1 = mdist.shard_range(n, rank, world)
+    q = full["queries"][q0:q1].clone().requires_grad_(True)
+    d = full["documents"][int(off[q0]):int(off[q1])].clone().requires_grad_(True)
+    lens = lens_host[q0:q1].to(dev)
+    sizes = []
+    for r in range(world):
+        a0, a1 = mdist.shard_range(n, r, world)
+        sizes.append((int(lens_host[a0:a1].sum()), a1 - a0, a1 - a0))
+    target = mdist.contrastive_targets(q1 - q0, device=dev, docs_per_rank=[s[1] for s in sizes])
+    peer = None
+    if args.transport == "peer":
+        from maxsim_b200.peer import PeerExchange
+        peer = PeerExchange(max_doc_tokens=max(s[0] for s in sizes), max_docs=max(s[1] for s in sizes),
+                            max_queries=max(s[2] for s in sizes), lq=q.shape[1], dim=q.shape[2],
+                            dtype=q.dtype, wait_polls=1 << 21)
+    records_group = dist.new_group(
+        backend="nccl", pg_options=dist.ProcessGroupNCCL.Options(is_high_priority_stream=True))
+
+    def step():
+        q.grad = None
+        d.grad = None
+        s = mdist.score_contrastive_sharded(q, d, lens, shard_sizes=sizes, records_group=records_group,
+                                            peer=peer)
+        (torch.nn.functional.cross_entropy(s, target, reduction="sum") / n).backward()
+
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize()
+    dist.barrier()
+    with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            step()
+        torch.cuda.synchronize()
+    events = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+                     and not e.name.startswith("nccl:")), key=lambda e: e.time_range.start)
+    per_step = len(events) // 3
+    last = events[-per_step:]
+    waits = [e.time_range.end - e.time_range.start for e in last if "peer_barrier" in e.name]
+    for r in range(world):
+        if r == rank:
+            if rank == 0:
+                base = last[0].time_range.start
+                print(f"# {world} GPUs, transport {args.transport}, global Nq = Nb = {n}; rank 0, last of 3 "
+                      "profiled steps; start us, duration us, kernel or copy", flush=True)
+                for e in last:
+                    print(f"{e.time_range.start - base:9.1f} {e.time_range.end - e.time_range.start:8.1f}  "
+                          f"{e.name[:72]}", flush=True)
+                print(f"# span {last[-1].time_range.end - base:.1f} us", flush=True)
+            print(f"# rank {rank}: barrier kernels waited " + " ".join(f"{w:.0f}" for w in waits) + " us",
+                  flush=True)
+        dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -1219,9 +1299,16 @@ def main():
                     help="run only train steps of the packed pair grid (65536 pairs); for profiler captures")
     ap.add_argument("--list-order", action="store_true",
                     help="with --profile-packed: visit pairs in list order, atomic backward")
+    ap.add_argument("--timeline-sharded", action="store_true",
+                    help="under torchrun: print the device timeline of one sharded contrastive train "
+                         "step (torch profiler; Nq=Nb=1024, or 256 with --small)")
+    ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
+                    help="with --timeline-sharded: how the shards and records travel")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+    elif args.timeline_sharded:
+        run_sharded_timeline(args)
     elif args.profile_contrastive:
         run_contrastive_profile(args)
     elif args.profile_packed:
