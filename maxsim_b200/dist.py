@@ -349,9 +349,7 @@ class _ShardedContrastive(torch.autograd.Function):
         docs_all = torch.empty((sum(tokens), d_local.shape[1]), dtype=d_local.dtype, device=dev)
         lens_all = torch.empty((col0[-1],), dtype=torch.int32, device=dev)
         q_all = torch.empty((sum(n_queries),) + tuple(q.shape[1:]), dtype=q.dtype, device=dev)
-        after_event, before_event, all_event = peer.gather(d_local, lens_local, q, sizes, docs_all,
-                                                           lens_all, q_all)
-        main = torch.cuda.current_stream(dev)
+        after, before, everything = peer.gather(d_local, lens_local, q, sizes, docs_all, lens_all, q_all)
         off_local = _offsets(ops, lens_local)
         offsets = _offsets(ops, lens_all)
         scores = torch.empty((q.shape[0], col0[-1]), dtype=torch.float32, device=dev)
@@ -363,15 +361,15 @@ class _ShardedContrastive(torch.autograd.Function):
             # it.  Each of the two runs is a contiguous range of columns and gets one launch
             # (the copies are far quicker than the block scored meanwhile, and every launch
             # pays its own ramp-up and tail).
-            for first, last, event in ((rank + 1, world, after_event), (0, rank, before_event)):
+            for first, last, landed in ((rank + 1, world, after), (0, rank, before)):
                 if col0[last] == col0[first]:
                     continue
-                main.wait_event(event)
+                landed.wait()
                 ops.contrastive_forward_block(q, docs_all, offsets[col0[first]:col0[last] + 1], scores,
                                               argmax, col0[first], sum(tokens[first:last]))
-            main.wait_event(all_event)  # every read of a peer's buffers is ordered before what follows
+            everything.wait()  # every read of a peer's buffers is ordered before what follows
         else:  # shape outside the block kernel: one ordinary call over all shards
-            main.wait_event(all_event)
+            everything.wait()
             scores, argmax = ops.maxsim_contrastive_forward_with_argmax(q, docs_all, offsets)
         ctx.save_for_backward(q, docs_all, offsets, argmax, d_local, off_local)
         ctx.q_all, ctx.h_q = q_all, _Done()
@@ -473,7 +471,7 @@ def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, op
     buffers (copy engines; the forward launches keep every SM) and the argmax
     records as stores of the regrouping kernel into the owners' memory, with
     one barrier kernel per pass instead of collectives.  Needs
-    ``shard_sizes``, ``exchange="owner"`` and CUDA tensors.
+    ``shard_sizes`` and ``exchange="owner"``.
 
     ``exchange`` selects how the backward pass gets that sum to the owner:
     ``"owner"`` (default) sends each owner the argmax and score gradient of its
@@ -494,8 +492,8 @@ def score_contrastive_sharded(queries, documents, doc_lengths, *, group=None, op
     if exchange not in ("owner", "reduce_scatter"):
         raise ValueError(f"exchange must be 'owner' or 'reduce_scatter'; got {exchange!r}")
     if peer is not None:
-        if exchange != "owner" or shard_sizes is None or not queries.is_cuda:
-            raise ValueError("the peer transport needs exchange='owner', shard_sizes and CUDA tensors")
+        if exchange != "owner" or shard_sizes is None:
+            raise ValueError("the peer transport needs exchange='owner' and shard_sizes")
         if not hasattr(ops, "contrastive_forward_block"):
             raise ValueError("the peer transport needs the CUDA library's operators")
     return _ShardedContrastive.apply(queries, documents, doc_lengths, group, ops, exchange, shard_sizes,

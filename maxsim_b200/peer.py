@@ -40,6 +40,18 @@ from . import _ops
 __all__ = ["PeerExchange"]
 
 
+class _StreamWait:
+    """Handle of work on a side stream: ``wait()`` makes the current stream
+    wait for the event recorded behind it (no host wait)."""
+
+    def __init__(self, event, device):
+        self.event, self.device = event, device
+
+    def wait(self):
+        torch.cuda.current_stream(self.device).wait_event(self.event)
+        return True
+
+
 def _round_up(n: int, to: int = 256) -> int:
     return (n + to - 1) // to * to
 
@@ -140,10 +152,11 @@ class PeerExchange:
         travel as one copy-engine copy per owner on a side stream (the ranks
         after this one, then those before it); the queries and this rank's own
         rows follow on a second side stream.  Each group of copies is issued by
-        one call into the library.  Returns
-        ``(after_event, before_event, all_event)``: the documents of the ranks
-        after / before this one have landed; everything has.  The caller's
-        tensors must stay untouched until ``all_event`` has been waited for."""
+        one call into the library.  Returns three handles ``(after, before,
+        everything)`` whose ``wait()`` orders the current stream behind: the
+        documents of the ranks after this one, of those before it, everything.
+        The caller's tensors must stay untouched until ``everything`` has been
+        waited for."""
         rank, world = self.rank, self.world
         tokens = [s[0] for s in sizes]
         n_docs = [s[1] for s in sizes]
@@ -196,7 +209,8 @@ class PeerExchange:
             self._fetch_small.wait_event(before_event)
             all_event = plan["events"][3]
             all_event.record(self._fetch_small)
-        return after_event, before_event, all_event
+        return (_StreamWait(after_event, dev), _StreamWait(before_event, dev),
+                _StreamWait(all_event, dev))
 
     def _plan(self, slot, tokens, n_docs, n_queries):
         """Views, tables and events of one (slot, shard sizes) combination;

@@ -48,6 +48,66 @@ def _oracle_ops():
                                  maxsim_contrastive_backward=bwd)
 
 
+def _oracle_ops_with_blocks():
+    """The stand-in operators plus the column-block forward the peer transport
+    drives (same contract as the CUDA entry point: the block's offsets are rows
+    of ``d``, its columns start at ``col0`` of the wider outputs)."""
+    from oracle import maxsim_oracle as oracle
+    ops = _oracle_ops()
+
+    def block(q, d, block_offsets, scores, argmax, col0, block_tokens=0, reserve_sms=0):
+        off = block_offsets.numpy().astype(np.int64)
+        n = off.size - 1
+        rows = d.float().numpy()[off[0]:off[-1]]
+        s, a = oracle.score_contrastive(q.float().numpy(), rows, (off - off[0]).astype(np.int32))
+        scores[:, col0:col0 + n] = torch.from_numpy(s)
+        argmax[:, col0:col0 + n] = torch.from_numpy(a)
+        return True
+
+    ops.contrastive_forward_block = block
+    return ops
+
+
+class _HostPeer:
+    """What ``maxsim_b200.peer.PeerExchange`` does, with gloo collectives in
+    place of peer-mapped memory: the driver's use of the transport (which
+    columns are scored from which rows, where each rank's records land) runs
+    on CPU ranks."""
+
+    class _Done:
+        def wait(self):
+            return True
+
+    def __init__(self, group=None):
+        self.group = group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.barriers = 0
+
+    def check_fits(self, sizes, lq, dim, dtype):
+        assert len(sizes) == self.world
+
+    def barrier(self):
+        self.barriers += 1
+        dist.barrier(self.group)
+
+    def gather(self, documents, lengths, queries, sizes, docs_all, lens_all, q_all):
+        for out, local, col in ((docs_all, documents, 0), (lens_all, lengths, 1), (q_all, queries, 2)):
+            mdist._all_gather_rows(out, local.detach(), [s[col] for s in sizes], self.group, self.rank).wait()
+        return self._Done(), self._Done(), self._Done()
+
+    def send_records(self, argmax, dscore, col_start, sizes):
+        n_docs, n_queries = [s[1] for s in sizes], [s[2] for s in sizes]
+        col0 = col_start.tolist()
+        record = torch.cat([argmax.to(torch.int32), dscore.contiguous().view(torch.int32).unsqueeze(-1)], dim=2)
+        send = torch.cat([record[:, col0[o]:col0[o + 1]].reshape(-1) for o in range(self.world)])
+        width = argmax.shape[2] + 1
+        in_splits = [n * argmax.shape[0] * width for n in n_docs]
+        out_splits = [n_docs[self.rank] * nq * width for nq in n_queries]
+        recv = torch.empty((sum(out_splits),), dtype=torch.int32)
+        dist.all_to_all_single(recv, send, out_splits, in_splits, group=self.group)
+        return recv
+
+
 def _padded_scorer(q, d, ql, dl):
     from oracle import maxsim_oracle as oracle
     s, _ = oracle.score_candidates_padded(q.float().numpy(), d.float().numpy(), ql.numpy(), dl.numpy())
@@ -78,13 +138,24 @@ def _contrastive_worker(rank, world, port, out_dir, exchange):
                 a0, a1 = mdist.shard_range(11, r, world)
                 b0, b1 = mdist.shard_range(12, r, world)
                 sizes.append((int(wl.document_offsets[a1] - wl.document_offsets[a0]), a1 - a0, b1 - b0))
-        s = mdist.score_contrastive_sharded(q, d, torch.from_numpy(lens[d0:d1]), ops=_oracle_ops(),
-                                            exchange=exchange, shard_sizes=sizes)
+        peer = None
+        if exchange == "peer":  # the owner exchange over the transport object
+            exchange, peer = "owner", _HostPeer()
+            sizes = []
+            for r in range(world):
+                a0, a1 = mdist.shard_range(11, r, world)
+                b0, b1 = mdist.shard_range(12, r, world)
+                sizes.append((int(wl.document_offsets[a1] - wl.document_offsets[a0]), a1 - a0, b1 - b0))
+        s = mdist.score_contrastive_sharded(q, d, torch.from_numpy(lens[d0:d1]),
+                                            ops=_oracle_ops_with_blocks() if peer else _oracle_ops(),
+                                            exchange=exchange, shard_sizes=sizes, peer=peer)
         g = torch.from_numpy(np.random.default_rng(5).standard_normal((12, 11)).astype(np.float32))
         (s * g[q0:q1]).sum().backward()
         docs_per_rank = [mdist.shard_range(11, r, world)[1] - mdist.shard_range(11, r, world)[0]
                          for r in range(world)]
         tgt = mdist.contrastive_targets(q1 - q0, docs_per_rank=docs_per_rank)
+        if peer is not None:
+            assert peer.barriers == 1  # the backward pass orders the records with one barrier
         np.savez(Path(out_dir) / f"r{rank}.npz", s=s.detach().numpy(), dq=q.grad.numpy(),
                  dd=d.grad.numpy(), tgt=tgt.numpy())
     finally:
@@ -92,7 +163,8 @@ def _contrastive_worker(rank, world, port, out_dir, exchange):
 
 
 @pytest.mark.parametrize("world,exchange", [(2, "owner"), (3, "owner"), (5, "owner"),  # 5: uneven query shards
-                                            (2, "reduce_scatter"), (3, "reduce_scatter")])
+                                            (2, "reduce_scatter"), (3, "reduce_scatter"),
+                                            (2, "peer"), (3, "peer"), (5, "peer")])
 def test_contrastive_sharded_matches_unsharded(world, exchange, tmp_path):
     from oracle import maxsim_oracle as oracle
     port = _free_port()
