@@ -61,7 +61,7 @@ import torch.distributed as dist
 
 __all__ = [
     "shard_range", "score_candidates_padded_sharded", "score_contrastive_sharded",
-    "contrastive_targets", "offsets_from_lengths",
+    "contrastive_targets", "offsets_from_lengths", "fetch_schedule",
 ]
 
 
@@ -264,6 +264,52 @@ def _offsets(ops, lengths: torch.Tensor) -> torch.Tensor:
     return fn(lengths) if fn is not None and lengths.is_cuda else offsets_from_lengths(lengths)
 
 
+def fetch_schedule(rank: int, tokens: Sequence[int], n_queries_local: int, lq: int, dim: int,
+                   itemsize: int) -> List[Tuple[int, int]]:
+    """Which fetched shards a rank scores with which launch, for the peer
+    transport: contiguous rank ranges ``(first, last)`` in the order the shards
+    are fetched (the ranks after ``rank``, then those before it).
+
+    Every launch pays a ramp-up and a tail, so few launches are better -- as
+    long as none waits for its data.  The shards arrive one after the other
+    while the rank's own block and then the earlier ranges are being scored;
+    the schedule is what a greedy consumer would do: each launch takes every
+    shard that has landed by the time the previous launch ends (at least one).
+    With shards that arrive faster than they are scored (4 GPUs on config 5:
+    30 us against 185 us) that is one launch for everything fetched; with
+    many small shards (8 GPUs: the seven copies take 180 us, a block 45 us)
+    it is a short first launch followed by longer ones.  The rates are the
+    measured ones of this library on a B200 (copy-engine fetch over NVLink,
+    forward with argmax); they only steer the grouping."""
+    world = len(tokens)
+    order = [(rank + k) % world for k in range(1, world)]
+    copy_rate, copy_latency = 4.0e11, 2.0e-6        # bytes/s per fetch, s per copy
+    score_rate, launch_cost = 1.0e15, 12.0e-6       # flop/s of forward + argmax, s per launch
+    per_token = 2.0 * n_queries_local * lq * dim / score_rate
+    landed, t = [], 0.0
+    for r in order:
+        t += tokens[r] * dim * itemsize / copy_rate + copy_latency
+        landed.append(t)
+    now = tokens[rank] * per_token + launch_cost   # the own block ends
+    groups, k = [], 0
+    while k < len(order):
+        n = max(1, sum(1 for x in landed[k:] if x <= now))
+        group = order[k:k + n]
+        now = max(now, landed[k + n - 1]) + sum(tokens[r] for r in group) * per_token + launch_cost
+        groups.append(group)
+        k += n
+    ranges = []
+    for group in groups:  # a group that wraps around the last rank is two column ranges
+        first = prev = group[0]
+        for r in group[1:]:
+            if r != prev + 1:
+                ranges.append((first, prev + 1))
+                first = r
+            prev = r
+        ranges.append((first, prev + 1))
+    return ranges
+
+
 class _ShardedContrastive(torch.autograd.Function):
     @staticmethod
     def forward(ctx, queries, documents, doc_lengths, group, ops, exchange, shard_sizes, records_group,
@@ -349,7 +395,8 @@ class _ShardedContrastive(torch.autograd.Function):
         docs_all = torch.empty((sum(tokens), d_local.shape[1]), dtype=d_local.dtype, device=dev)
         lens_all = torch.empty((col0[-1],), dtype=torch.int32, device=dev)
         q_all = torch.empty((sum(n_queries),) + tuple(q.shape[1:]), dtype=q.dtype, device=dev)
-        after, before, everything = peer.gather(d_local, lens_local, q, sizes, docs_all, lens_all, q_all)
+        ranges = fetch_schedule(rank, tokens, q.shape[0], q.shape[1], q.shape[2], q.element_size())
+        landed, everything = peer.gather(d_local, lens_local, q, sizes, docs_all, lens_all, q_all, ranges)
         off_local = _offsets(ops, lens_local)
         offsets = _offsets(ops, lens_all)
         scores = torch.empty((q.shape[0], col0[-1]), dtype=torch.float32, device=dev)
@@ -357,14 +404,12 @@ class _ShardedContrastive(torch.autograd.Function):
         blocks = ops.contrastive_forward_block(q, d_local, off_local, scores, argmax, col0[rank],
                                                tokens[rank])
         if blocks:
-            # the shards arrive in ring order: those after this rank's own, then those before
-            # it.  Each of the two runs is a contiguous range of columns and gets one launch
-            # (the copies are far quicker than the block scored meanwhile, and every launch
-            # pays its own ramp-up and tail).
-            for first, last, landed in ((rank + 1, world, after), (0, rank, before)):
+            # every range of fetched shards is a contiguous range of columns and gets one
+            # launch, as soon as its last shard has landed (see fetch_schedule)
+            for (first, last), handle in zip(ranges, landed):
+                handle.wait()
                 if col0[last] == col0[first]:
                     continue
-                landed.wait()
                 ops.contrastive_forward_block(q, docs_all, offsets[col0[first]:col0[last] + 1], scores,
                                               argmax, col0[first], sum(tokens[first:last]))
             everything.wait()  # every read of a peer's buffers is ordered before what follows

@@ -142,21 +142,22 @@ class PeerExchange:
 
     # -- forward -------------------------------------------------------------
 
-    def gather(self, documents, lengths, queries, sizes, docs_all, lens_all, q_all):
+    def gather(self, documents, lengths, queries, sizes, docs_all, lens_all, q_all, ranges=None):
         """Publish this rank's shard and gather all shards into the
         rank-ordered ``docs_all [T_total, D]``, ``lens_all [Nb_total]`` and
         ``q_all [Nq_total, Lq, D]``.
 
         The lengths are complete on the current stream when this returns (one
         small kernel reads them out of the peers' buffers).  The documents
-        travel as one copy-engine copy per owner on a side stream (the ranks
-        after this one, then those before it); the queries and this rank's own
-        rows follow on a second side stream.  Each group of copies is issued by
-        one call into the library.  Returns three handles ``(after, before,
-        everything)`` whose ``wait()`` orders the current stream behind: the
-        documents of the ranks after this one, of those before it, everything.
-        The caller's tensors must stay untouched until ``everything`` has been
-        waited for."""
+        travel as one copy-engine copy per owner on a side stream, range by
+        range: ``ranges`` lists contiguous rank ranges ``(first, last)`` in the
+        order to fetch them (default: the ranks after this one, then those
+        before it); the queries and this rank's own rows follow on a second
+        side stream.  The copies of a range are issued by one call into the
+        library.  Returns ``(landed, everything)``: one handle per range and
+        one for all transfers, whose ``wait()`` orders the current stream
+        behind them.  The caller's tensors must stay untouched until
+        ``everything`` has been waited for."""
         rank, world = self.rank, self.world
         tokens = [s[0] for s in sizes]
         n_docs = [s[1] for s in sizes]
@@ -182,23 +183,30 @@ class PeerExchange:
         d_base, q_base = docs_all.data_ptr(), q_all.data_ptr()
         row, q0 = plan["row0"], plan["q0"]
         q_bytes = self.lq * row_bytes
+        if ranges is None:
+            ranges = [(rank + 1, world), (0, rank)]
+        covered = sorted(r for first, last in ranges for r in range(first, last))
+        if covered != [r for r in range(world) if r != rank]:
+            raise ValueError(f"ranges {ranges} must cover every rank but {rank} exactly once")
+        events = plan["events"]
+        while len(events) < 2 + len(ranges):
+            events.append(torch.cuda.Event())
+        landed = []
         with torch.cuda.stream(self._fetch_docs):
             self._fetch_docs.wait_event(ready)
-            after = range(rank + 1, world)
-            _ops.copy_many([d_base + row[r] * row_bytes for r in after],
-                           [plan["docs_src"][r] for r in after],
-                           [tokens[r] * row_bytes for r in after], dev)
-            after_event = plan["events"][1]
-            after_event.record(self._fetch_docs)
-            before = range(0, rank)
-            _ops.copy_many([d_base + row[r] * row_bytes for r in before],
-                           [plan["docs_src"][r] for r in before],
-                           [tokens[r] * row_bytes for r in before], dev)
-            before_event = plan["events"][2]
-            before_event.record(self._fetch_docs)
+            for k, (first, last) in enumerate(ranges):
+                span = range(first, last)
+                _ops.copy_many([d_base + row[r] * row_bytes for r in span],
+                               [plan["docs_src"][r] for r in span],
+                               [tokens[r] * row_bytes for r in span], dev)
+                events[2 + k].record(self._fetch_docs)
+                landed.append(_StreamWait(events[2 + k], dev))
+            last_docs = events[2 + len(ranges) - 1] if ranges else ready
         with torch.cuda.stream(self._fetch_small):
-            self._fetch_small.wait_event(ready)
-            # needed by the backward pass only: all queries, this rank's own document rows
+            # needed by the backward pass only: all queries, this rank's own document rows.
+            # Behind the documents: the copy engine serves one peer copy at a time, and the
+            # forward launches wait for the documents.
+            self._fetch_small.wait_event(last_docs)
             others = [r for r in range(world) if r != rank]
             _ops.copy_many(
                 [q_base + q0[r] * q_bytes for r in others] + [q_base + q0[rank] * q_bytes,
@@ -206,11 +214,9 @@ class PeerExchange:
                 [plan["q_src"][r] for r in others] + [queries.data_ptr(), documents.data_ptr()],
                 [n_queries[r] * q_bytes for r in others] + [n_queries[rank] * q_bytes,
                                                             tokens[rank] * row_bytes], dev)
-            self._fetch_small.wait_event(before_event)
-            all_event = plan["events"][3]
+            all_event = events[1]
             all_event.record(self._fetch_small)
-        return (_StreamWait(after_event, dev), _StreamWait(before_event, dev),
-                _StreamWait(all_event, dev))
+        return landed, _StreamWait(all_event, dev)
 
     def _plan(self, slot, tokens, n_docs, n_queries):
         """Views, tables and events of one (slot, shard sizes) combination;
@@ -239,7 +245,7 @@ class PeerExchange:
             "q0": q0,
             "lens_table": torch.tensor(lens_rows, dtype=torch.int64, device=self.device).reshape(len(lens_rows), 4),
             "lens_max": max([4 * n for n in n_docs] + [0]),
-            "events": [torch.cuda.Event() for _ in range(4)],
+            "events": [torch.cuda.Event() for _ in range(2)],  # ready, everything; one per range follows
         }
         self._tables[key] = plan
         return plan

@@ -90,10 +90,13 @@ class _HostPeer:
         self.barriers += 1
         dist.barrier(self.group)
 
-    def gather(self, documents, lengths, queries, sizes, docs_all, lens_all, q_all):
+    def gather(self, documents, lengths, queries, sizes, docs_all, lens_all, q_all, ranges=None):
+        others = sorted(r for first, last in ranges for r in range(first, last))
+        assert others == [r for r in range(self.world) if r != self.rank]
+        self.ranges = list(ranges)
         for out, local, col in ((docs_all, documents, 0), (lens_all, lengths, 1), (q_all, queries, 2)):
             mdist._all_gather_rows(out, local.detach(), [s[col] for s in sizes], self.group, self.rank).wait()
-        return self._Done(), self._Done(), self._Done()
+        return [self._Done() for _ in ranges], self._Done()
 
     def send_records(self, argmax, dscore, col_start, sizes):
         n_docs, n_queries = [s[1] for s in sizes], [s[2] for s in sizes]
@@ -258,3 +261,18 @@ def test_argument_checks():
     # world size 1 needs no process group
     s = mdist.score_contrastive_sharded(q, d, torch.tensor([2, 4]), ops=_oracle_ops())
     assert s.shape == (2, 2)
+
+
+def test_fetch_schedule_covers_every_other_rank_in_fetch_order():
+    # many small shards: several launches, the first ones short; few large ones: one launch
+    for world, tokens, nq in ((8, [37000] * 8, 128), (4, [74000] * 4, 256), (2, [150000] * 2, 512),
+                              (5, [900, 40000, 10, 70000, 3000], 7), (3, [5, 5, 5], 1)):
+        for rank in range(world):
+            ranges = mdist.fetch_schedule(rank, tokens, nq, 32, 128, 2)
+            order = [r for first, last in ranges for r in range(first, last)]
+            assert order == [(rank + k) % world for k in range(1, world)], (world, rank, ranges)
+            assert all(0 <= first < last <= world for first, last in ranges)
+    assert mdist.fetch_schedule(0, [74000] * 4, 256, 32, 128, 2) == [(1, 4)]
+    assert mdist.fetch_schedule(1, [74000] * 4, 256, 32, 128, 2) == [(2, 4), (0, 1)]
+    eight = mdist.fetch_schedule(0, [37000] * 8, 128, 32, 128, 2)
+    assert 2 <= len(eight) <= 4 and eight[0][1] - eight[0][0] <= 2, eight
